@@ -51,6 +51,13 @@ __device__ __forceinline__ float kp_act_epilogue(int act, float g) {
     if (act == KP_ACT_GELU_TANH) return kp_act<KP_ACT_GELU_TANH>(g);
     return g / (1.0f + expf(-g));
 }
+// The gated unit with limits (a design's own activation, with its constants as arguments): the gate is bounded above,
+// the other branch on both sides, and the unit is g sigmoid(alpha g) (u + shift).
+__device__ __forceinline__ float kp_glu_clamped(float g, float u, float limit, float alpha, float shift) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g / (1.0f + expf(-alpha * g))) * (u + shift);
+}
 #define KP_EPI_ACT(epi) (((epi) >> 8) & 0xff)
 #define KP_EPI_KIND(epi) ((epi) & 0xff)
 

@@ -4,6 +4,9 @@
 //   o_t = S_t^T q_t
 //
 // with q, k, v = act(projection) (act = silu or none), read from columns of one wide row in the storage type.
+// Optionally q and k are rotated by position as they are staged (the first `rot` dimensions of a head, dimension i
+// paired with i + rot/2, cos and sin from tables [position][rot/2] made in double), and k is multiplied by a constant
+// behind the rotation; both in float32, so that what enters the recurrence was never rounded to the storage type.
 // Everything of the recurrence is float32: the state, the decay (carried as a float32 pair hi + lo so that a
 // thousand steps of it do not drift from the constant the model gives), the products and the sums.  The state of a
 // request lives in its slot between steps and counts as zero at position 0.
@@ -32,13 +35,20 @@ template <int ACT> __device__ __forceinline__ float lt_act(float z) {
     return ACT == 0 ? z / (1.0f + expf(-z)) : z;
 }
 
+// One element of a rotated pair: `x` is the element itself, `y` its partner (i + rot/2 for the lower half, i - rot/2 for
+// the upper); (u, v) -> (u c - v s, v c + u s).
+__device__ __forceinline__ void lt_rotate(float& x, float y, float c, float s, bool lower) {
+    x = lower ? x * c - y * s : x * c + y * s;
+}
+
 // R: key rows a thread keeps (dim <= LT_PARTS * R).  Thread (part p, column c) owns rows p R .. p R + R - 1 of column c.
 template <typename T, int R, int ACT>
 __global__ void __launch_bounds__(LT_THREADS)
 lightning_scan_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay_hi,
                       const float* __restrict__ decay_lo, float* __restrict__ state, const int* __restrict__ cu_rows,
                       const int* __restrict__ seg_pos, const int* __restrict__ seg_slot, float* __restrict__ o, int ldo, int H,
-                      int dim, int vdim, int write_state) {
+                      int dim, int vdim, int write_state, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                      int rot, float k_scale) {
     kp_pdl_begin();
     constexpr int DP = LT_PARTS * R;                             // the key rows, padded with zeros
     constexpr int LT_CH = R >= 16 ? LT_CH_MAX / 2 : LT_CH_MAX;
@@ -70,6 +80,14 @@ lightning_scan_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, i
                 const T* row = qkv + (size_t)(t0 + t) * ld + head * dim + i;
                 qv = lt_act<ACT>(to_f32(row[q_col]));
                 kv = lt_act<ACT>(to_f32(row[k_col]));
+                if (i < rot) {
+                    const int half = rot >> 1, lowr = i < half;
+                    const T* prow = lowr ? row + half : row - half;
+                    const size_t tb = (size_t)(seg_pos[seg] + (t0 + t - row0)) * half + (lowr ? i : i - half);
+                    lt_rotate(qv, lt_act<ACT>(to_f32(prow[q_col])), cos_tab[tb], sin_tab[tb], lowr);
+                    lt_rotate(kv, lt_act<ACT>(to_f32(prow[k_col])), cos_tab[tb], sin_tab[tb], lowr);
+                }
+                kv *= k_scale;
             }
             sq[t][i] = qv;
             sk[t][i] = kv;
@@ -140,23 +158,51 @@ lightning_scan_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, i
 
 // A [rows t0 .. t0 + n) x [dim] stretch of columns, with the activation, transposed into dst [dim][LC_LD]
 // (zeros behind the n rows).
+// What staging needs to rotate and scale q or k: the tables, the rotated dimensions (0: none), the position of the
+// chunk's first row and the constant factor.
+struct LcRot { const float* cos_tab; const float* sin_tab; int rot; int pos0; float scale; };
+
 template <typename T, int ACT, bool VEC>
 __device__ __forceinline__ void lc_stage_transposed(float* dst, const T* __restrict__ qkv, int ld, int col, int head, int dim,
-                                                    int t0, int n, int tid) {
-    if (VEC) {
+                                                    int t0, int n, int tid, const LcRot rp) {
+    const int half = rp.rot >> 1;
+    if (VEC && (half % 8 == 0)) {
         const int ng = dim / 8;
         for (int x = tid; x < ng * LC_C; x += LC_THREADS) {
             const int t = x % LC_C, g = x / LC_C;
-            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-            if (t < n) raw = __ldg(reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + t) * ld + col + head * dim + g * 8));
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u), praw = raw;
+            const bool rotated = g * 8 < rp.rot, lowr = g * 8 < half;
+            if (t < n) {
+                const T* src = qkv + (size_t)(t0 + t) * ld + col + head * dim + g * 8;
+                raw = __ldg(reinterpret_cast<const uint4*>(src));
+                if (rotated) praw = __ldg(reinterpret_cast<const uint4*>(lowr ? src + half : src - half));
+            }
             const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
+            const bf16* p8 = reinterpret_cast<const bf16*>(&praw);
 #pragma unroll
-            for (int e = 0; e < 8; e++) dst[(g * 8 + e) * LC_LD + t] = t < n ? lt_act<ACT>(__bfloat162float(e8[e])) : 0.f;
+            for (int e = 0; e < 8; e++) {
+                float v = t < n ? lt_act<ACT>(__bfloat162float(e8[e])) : 0.f;
+                if (rotated && t < n) {
+                    const size_t tb = (size_t)(rp.pos0 + t) * half + (lowr ? g * 8 + e : g * 8 + e - half);
+                    lt_rotate(v, lt_act<ACT>(__bfloat162float(p8[e])), rp.cos_tab[tb], rp.sin_tab[tb], lowr);
+                }
+                dst[(g * 8 + e) * LC_LD + t] = v * rp.scale;
+            }
         }
     } else {
         for (int x = tid; x < dim * LC_C; x += LC_THREADS) {
             const int t = x % LC_C, d = x / LC_C;
-            dst[d * LC_LD + t] = t < n ? lt_act<ACT>(to_f32(qkv[(size_t)(t0 + t) * ld + col + head * dim + d])) : 0.f;
+            float v = 0.f;
+            if (t < n) {
+                const T* src = qkv + (size_t)(t0 + t) * ld + col + head * dim + d;
+                v = lt_act<ACT>(to_f32(*src));
+                if (d < rp.rot) {
+                    const bool lowr = d < half;
+                    const size_t tb = (size_t)(rp.pos0 + t) * half + (lowr ? d : d - half);
+                    lt_rotate(v, lt_act<ACT>(to_f32(lowr ? src[half] : src[-half])), rp.cos_tab[tb], rp.sin_tab[tb], lowr);
+                }
+            }
+            dst[d * LC_LD + t] = v * rp.scale;
         }
     }
 }
@@ -175,7 +221,9 @@ template <typename T, int ACT, bool VEC>
 __global__ void __launch_bounds__(LC_THREADS)
 lightning_chunk_sums_kernel(const T* __restrict__ qkv, int ld, int k_col, int v_col, const float* __restrict__ decay_pow,
                             const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg,
-                            const int* __restrict__ chunk_row0, float* __restrict__ U, int H, int dim, int vdim) {
+                            const int* __restrict__ chunk_row0, float* __restrict__ U, int H, int dim, int vdim,
+                            const int* __restrict__ seg_pos, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                            int rot, float k_scale) {
     kp_pdl_begin();
     extern __shared__ __align__(16) float lc_sm[];
     float* Kt = lc_sm;                                           // [dim][LC_LD]
@@ -183,7 +231,9 @@ lightning_chunk_sums_kernel(const T* __restrict__ qkv, int ld, int k_col, int v_
     float* kw = Vs + LC_C * LC_COLS;                             // [LC_C]
     const int chunk = blockIdx.x, head = blockIdx.y, tile = blockIdx.z, tid = threadIdx.x;
     const int t0 = chunk_row0[chunk], n = min(LC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
-    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid);
+    const int sg = chunk_seg[chunk];
+    const LcRot rk = {cos_tab, sin_tab, rot, rot ? seg_pos[sg] + t0 - cu_rows[sg] : 0, k_scale};
+    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid, rk);
     lc_stage_values<T, ACT>(Vs, qkv, ld, v_col, head, vdim, tile, t0, n, tid);
     for (int x = tid; x < LC_C; x += LC_THREADS) kw[x] = x < n ? decay_pow[(size_t)head * (LC_C + 1) + n - 1 - x] : 0.f;
     __syncthreads();
@@ -261,7 +311,9 @@ template <typename T, int ACT, bool VEC>
 __global__ void __launch_bounds__(LC_THREADS)
 lightning_chunk_out_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay_pow,
                            const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg, const int* __restrict__ chunk_row0,
-                           const float* __restrict__ U, float* __restrict__ o, int ldo, int H, int dim, int vdim) {
+                           const float* __restrict__ U, float* __restrict__ o, int ldo, int H, int dim, int vdim,
+                           const int* __restrict__ seg_pos, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                           int rot, float k_scale) {
     kp_pdl_begin();
     extern __shared__ __align__(16) float lc_sm[];
     float* Qt = lc_sm;                                           // [dim][LC_LD]
@@ -272,8 +324,11 @@ lightning_chunk_out_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_c
     float* pw = Ss + (size_t)dim * LC_COLS;                      // [LC_C + 1]
     const int chunk = blockIdx.x, head = blockIdx.y, tile = blockIdx.z, tid = threadIdx.x;
     const int t0 = chunk_row0[chunk], n = min(LC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
-    lc_stage_transposed<T, ACT, VEC>(Qt, qkv, ld, q_col, head, dim, t0, n, tid);
-    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid);
+    const int sg = chunk_seg[chunk];
+    const int pos0 = rot ? seg_pos[sg] + t0 - cu_rows[sg] : 0;
+    const LcRot rq = {cos_tab, sin_tab, rot, pos0, 1.0f}, rk = {cos_tab, sin_tab, rot, pos0, k_scale};
+    lc_stage_transposed<T, ACT, VEC>(Qt, qkv, ld, q_col, head, dim, t0, n, tid, rq);
+    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid, rk);
     lc_stage_values<T, ACT>(Vs, qkv, ld, v_col, head, vdim, tile, t0, n, tid);
     const float* Sc = U + ((size_t)chunk * H + head) * dim * vdim;
     for (int x = tid; x < dim * LC_COLS; x += LC_THREADS) {
@@ -357,17 +412,21 @@ extern "C" {
 // qkv: rows [n, ld] in the storage type; q, k at columns q_col, k_col (H heads of dim), v at v_col (H heads of vdim).
 // decay_hi + decay_lo: the heads' decays [H].  state: [slots, H, dim, vdim] float32.  o: [n, ldo] float32, heads side by
 // side.  act: 0 silu on q, k and v; 1 none.  Segments as everywhere: cu_rows [n_seg + 1], seg_pos, seg_slot [n_seg].
+// cos_tab, sin_tab [positions][rot / 2] and rot (even, at most dim; 0 and null tables: no rotation); k_scale: the factor
+// on k behind the rotation (1 for none).
 int kp_lightning_scan(const void* qkv, int ld, int q_col, int k_col, int v_col, const float* decay_hi, const float* decay_lo,
                       float* state, const int* cu_rows, const int* seg_pos, const int* seg_slot, float* o, int ldo, int n_seg,
-                      int H, int dim, int vdim, int act, int write_state, int dtype, void* stream) {
+                      int H, int dim, int vdim, int act, int write_state, const float* cos_tab, const float* sin_tab, int rot,
+                      float k_scale, int dtype, void* stream) {
     if (n_seg <= 0) return 0;
     if (H < 1 || dim < 1 || vdim < 1 || act < 0 || act > 1) return KP_ERR_BAD_ARG;
+    if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && (!cos_tab || !sin_tab))) return KP_ERR_BAD_ARG;
     if (dim > 16 * LT_PARTS || H > 65535 || (vdim + LT_COLS - 1) / LT_COLS > 65535) return KP_ERR_UNSUPPORTED;
     const dim3 grid(n_seg, H, (vdim + LT_COLS - 1) / LT_COLS), block(LT_THREADS);
     cudaStream_t s = (cudaStream_t)stream;
 #define LT_LAUNCH(T, R, ACT)                                                                                                 \
     kp_launch_pdl(lightning_scan_kernel<T, R, ACT>, grid, block, 0, s, (const T*)qkv, ld, q_col, k_col, v_col, decay_hi, decay_lo, \
-                  state, cu_rows, seg_pos, seg_slot, o, ldo, H, dim, vdim, write_state)
+                  state, cu_rows, seg_pos, seg_slot, o, ldo, H, dim, vdim, write_state, cos_tab, sin_tab, rot, k_scale)
     // (the rows a thread keeps depend on the head's size only, so a row's sums have the same order in every launch)
 #define LT_BY_R(T, ACT)                                                                                                      \
     do {                                                                                                                     \
@@ -392,9 +451,11 @@ int kp_lightning_chunk_rows() { return LC_C; }
 int kp_lightning_chunks(const void* qkv, int ld, int q_col, int k_col, int v_col, const float* decay_pow, float* state,
                         const int* cu_rows, const int* seg_pos, const int* seg_slot, const int* chunk_seg, const int* chunk_row0,
                         const int* seg_chunk0, int n_chunks, float* scratch, float* o, int ldo, int n_seg, int H, int dim, int vdim,
-                        int act, int write_state, int dtype, void* stream) {
+                        int act, int write_state, const float* cos_tab, const float* sin_tab, int rot, float k_scale, int dtype,
+                        void* stream) {
     if (n_seg <= 0 || n_chunks <= 0) return 0;
     if (H < 1 || dim < 1 || vdim < 1 || act < 0 || act > 1) return KP_ERR_BAD_ARG;
+    if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && (!cos_tab || !sin_tab))) return KP_ERR_BAD_ARG;
     const int tiles = (vdim + LC_COLS - 1) / LC_COLS;
     if (dim > LC_MAX_DIM || H > 65535 || tiles > 65535 || (dim * vdim + 255) / 256 > 65535) return KP_ERR_UNSUPPORTED;
     const size_t sm1 = ((size_t)dim * LC_LD + LC_C * LC_COLS + LC_C) * sizeof(float);
@@ -406,13 +467,13 @@ int kp_lightning_chunks(const void* qkv, int ld, int q_col, int k_col, int v_col
         if ((e = cudaFuncSetAttribute(lightning_chunk_sums_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e; \
         if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e; \
         kp_launch_pdl(lightning_chunk_sums_kernel<T, ACT, VEC>, dim3(n_chunks, H, tiles), dim3(LC_THREADS), sm1, s, (const T*)qkv, ld, \
-                      k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, scratch, H, dim, vdim);                       \
+                      k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, scratch, H, dim, vdim, seg_pos, cos_tab, sin_tab, rot, k_scale);                      \
         if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;                                                          \
         kp_launch_pdl(lightning_chunk_states_kernel, dim3(n_seg, H, (dim * vdim + 255) / 256), dim3(256), 0, s, scratch, decay_pow, \
                       state, cu_rows, seg_pos, seg_slot, seg_chunk0, chunk_row0, H, dim, vdim, write_state);                 \
         if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;                                                          \
         kp_launch_pdl(lightning_chunk_out_kernel<T, ACT, VEC>, dim3(n_chunks, H, tiles), dim3(LC_THREADS), sm3, s, (const T*)qkv, ld, \
-                      q_col, k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, (const float*)scratch, o, ldo, H, dim, vdim); \
+                      q_col, k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, (const float*)scratch, o, ldo, H, dim, vdim, seg_pos, cos_tab, sin_tab, rot, k_scale); \
     } while (0)
     const bool vec = dtype == KP_DTYPE_BF16 && dim % 8 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && !((uintptr_t)qkv & 15);
     if (vec) {

@@ -191,3 +191,61 @@ extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, con
         (T*)cache, page_size, H, G, hd, write_kv, v_col)));
     return kp_launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// The norm over whole projections: q and k are RMS-normed each as one row over all their heads at once,
+//   q <- q * rsqrt(sum(q^2) / count_q + eps) * w_q        (w_q as long as the projection; the same for k)
+// without any rotation; q goes to q_out, k (normed) and v (as it is) to the page and offset given by slot_map.
+// A head may be stored wider than it is (zero columns behind its own, as the weights' zero rows leave them), so the
+// counts of the means are arguments of their own.  write_kv == 0: a layer that reads another layer's keys and values
+// norms its queries only.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rownorm_kv_kernel(const T* __restrict__ qkv, int ld, int k_col, int v_col, const float* __restrict__ q_w,
+                     const float* __restrict__ k_w, float eps, float count_q, float count_k, const int* __restrict__ slot_map,
+                     T* __restrict__ q_out, int ldq, T* __restrict__ cache, int page_size, int H, int G, int hd, int write_kv) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int row = blockIdx.x;
+    const T* src = qkv + (size_t)row * ld;
+    const int nq = H * hd, nk = G * hd;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float v = to_f32(src[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float sq = 1.0f / sqrtf(ss / count_q + eps);
+    for (int i = threadIdx.x; i < nq; i += blockDim.x)
+        q_out[(size_t)row * ldq + i] = from_f32<T>((to_f32(src[i]) * sq) * q_w[i]);
+    if (!write_kv) return;
+    const int slot = slot_map[row];
+    float sk = 0.f;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const float v = to_f32(src[k_col + i]);
+        sk = fmaf(v, v, sk);
+    }
+    sk = block_sum(sk, red);
+    if (slot < 0) return;
+    const float scale_k = 1.0f / sqrtf(sk / count_k + eps);
+    const int page = slot / page_size, off = slot % page_size;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int g = i / hd, c = i - g * hd;
+        T* kd = cache + ((((size_t)page * 2 + 0) * G + g) * page_size + off) * hd + c;
+        T* vd = cache + ((((size_t)page * 2 + 1) * G + g) * page_size + off) * hd + c;
+        *kd = from_f32<T>((to_f32(src[k_col + i]) * scale_k) * k_w[i]);
+        *vd = src[v_col + i];
+    }
+}
+
+extern "C" int kp_qk_rownorm_kv(const void* qkv, int ld, int k_col, int v_col, const float* q_w, const float* k_w, float eps,
+                                float count_q, float count_k, const int* slot_map, void* q_out, int ldq, void* cache,
+                                int page_size, int n, int H, int G, int hd, int write_kv, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (H < 1 || G < 1 || hd < 1 || !q_w || !q_out || (write_kv && (!k_w || !cache || !slot_map))) return KP_ERR_BAD_ARG;
+    if (!(count_q > 0.f) || !(count_k > 0.f)) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(qk_rownorm_kv_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)qkv, ld,
+                                               k_col, v_col, q_w, k_w, eps, count_q, count_k, slot_map, (T*)q_out, ldq, (T*)cache,
+                                               page_size, H, G, hd, write_kv)));
+    return kp_launch_status();
+}

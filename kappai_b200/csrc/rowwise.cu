@@ -401,6 +401,100 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, siz
         out[i] = from_f32<TO>(to_f32(in[i]));
 }
 
+// A weighted layer norm without a shift: y[r,:] = (x[row,:] - mean) / sqrt(var + eps) * w, var the mean of the squared
+// deviations (taken about the mean, in a second pass over the row, not as a difference of two sums).  row = rows ?
+// rows[r] : r.  float32 statistics with a fixed tree.
+template <typename T>
+__global__ void __launch_bounds__(256)
+layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                      const int* __restrict__ rows, int d, float eps) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(rows ? rows[r] : r) * d;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) s += src[i];
+    const float mean = block_sum(s, red) / (float)d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = src[i] - mean;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    T* dst = y + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(((src[i] - mean) * scale) * w[i]);
+}
+
+// RMS norm of float32 rows cut into `groups` stretches of equal width, every stretch with a mean square of its own,
+// and a gate from rows in the storage type: gate_first ? norm(o * act(g)) * w : norm(o) * w * act(g); w may be null (no weight); act is silu
+// (gate_act 0) or the sigmoid (1).  A block takes one (row, part); its size depends on the part's width alone.
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_norm_gate_rows_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, const T* __restrict__ g, int ldg,
+                            T* __restrict__ out, int ldout, int width, float eps, int gate_first, int gate_act) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x, c0 = blockIdx.y * width;
+    const float* src = o + (size_t)r * ldo + c0;
+    const T* gr = g + (size_t)r * ldg + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = src[i];
+        if (gate_first) {
+            const float z = to_f32(gr[i]);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            v *= gate_act == 0 ? z * sg : sg;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float z = to_f32(gr[i]);
+        const float sg = 1.0f / (1.0f + expf(-z));
+        const float gate = gate_act == 0 ? z * sg : sg;
+        float v = gate_first ? (src[i] * gate) * scale : src[i] * scale;
+        if (w) v *= w[c0 + i];
+        if (!gate_first) v *= gate;
+        out[(size_t)r * ldout + c0 + i] = from_f32<T>(v);
+    }
+}
+
+// o[r, h * hd + i] *= sigmoid(g[r, h]): one gate a head.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ o, int ldo, const T* __restrict__ g, int ldg, int n, int H, int hd) {
+    kp_pdl_begin();
+    const size_t cols = (size_t)H * hd, total = (size_t)n * cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols, c = i % cols;
+        const float z = to_f32(g[r * ldg + c / hd]);
+        T* p = o + r * ldo + c;
+        *p = from_f32<T>(to_f32(*p) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+// x <- cap * tanh(x / cap), in place, float32 (a soft limit on logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    kp_pdl_begin();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+// The gated unit with limits: g = min(gate, limit), u = clamp(up, -limit, limit), act = g sigmoid(alpha g) (u + shift).
+// gate_up rows hold [gate(ff) | up(ff)].
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ act, int n, int ff, float limit, float alpha, float shift) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / ff, c = i % ff;
+        act[i] = from_f32<T>(kp_glu_clamped(to_f32(gu[r * 2 * ff + c]), to_f32(gu[r * 2 * ff + ff + c]), limit, alpha, shift));
+    }
+}
+
+
 static inline int grid_for(size_t total, int block) {
     size_t g = (total + block - 1) / block;
     if (g > 148 * 16) g = 148 * 16;
@@ -597,6 +691,49 @@ int kp_step_tables(const void* src, void* dst, int n_words, const int* tok_src, 
 int kp_gather_status(const unsigned long long* addrs, int n, int* out, void* stream) {
     if (n < 0 || !out) return KP_ERR_BAD_ARG;
     kp_launch_pdl(gather_status_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, addrs, n, out);
+    return kp_launch_status();
+}
+
+int kp_layernorm_rows(const float* x, const float* w, void* y, const int* rows, int n, int d, float eps, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(layernorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
+    return kp_launch_status();
+}
+
+// o: [n, ldo] float32, `groups` parts of `width` columns from column 0; g and out in the storage type `dtype`.
+int kp_group_norm_gate_rows(const float* o, int ldo, const float* w, const void* g, int ldg, void* out, int ldout, int n, int groups,
+                            int width, float eps, int gate_first, int gate_act, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (groups < 1 || width < 1 || gate_act < 0 || gate_act > 1) return KP_ERR_BAD_ARG;
+    if (groups > 65535) return KP_ERR_UNSUPPORTED;
+    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;      // by the part's width alone
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(group_norm_gate_rows_kernel<T>, dim3(n, groups), dim3(threads), 0, (cudaStream_t)stream, o,
+                                               ldo, w, (const T*)g, ldg, (T*)out, ldout, width, eps, gate_first, gate_act)));
+    return kp_launch_status();
+}
+
+int kp_head_gate(void* o, int ldo, const void* g, int ldg, int n, int H, int hd, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (H < 1 || hd < 1) return KP_ERR_BAD_ARG;
+    const int gr = grid_for((size_t)n * H * hd, 256);
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(head_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo, (const T*)g,
+                                               ldg, n, H, hd)));
+    return kp_launch_status();
+}
+
+int kp_softcap(float* x, long long n, float cap, void* stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return KP_ERR_BAD_ARG;
+    kp_launch_pdl(softcap_kernel, dim3(grid_for((size_t)n, 256)), dim3(256), 0, (cudaStream_t)stream, x, (size_t)n, cap);
+    return kp_launch_status();
+}
+
+int kp_glu_clamped(const void* gate_up, void* act, int n, int ff, float limit, float alpha, float shift, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    const int g = grid_for((size_t)n * ff, 256);
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(glu_clamped_kernel<T>, dim3(g), dim3(256), 0, (cudaStream_t)stream, (const T*)gate_up, (T*)act,
+                                               n, ff, limit, alpha, shift)));
     return kp_launch_status();
 }
 

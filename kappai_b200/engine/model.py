@@ -86,8 +86,14 @@ class Model:
     def cache_specs(self) -> List[Optional[object]]:
         """Per schedule entry: what its mixer keeps (None if nothing or borrowed)."""
         out = []
-        for e in self.schedule:
-            out.append(None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_spec())
+        for i, e in enumerate(self.schedule):
+            own = self.blocks[e.layer].mixer.cache_spec()
+            if e.cache_of is not None:
+                lent = self.blocks[self.schedule[e.cache_of].layer].mixer.cache_spec()
+                if own != lent:
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps {lent}, "
+                                     f"but its mixer works on {own}")
+            out.append(None if e.cache_of is not None else own)
         return out
 
     def cache_borrowing(self) -> List[Optional[int]]:

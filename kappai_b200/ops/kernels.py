@@ -298,6 +298,84 @@ def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def layernorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = (x - mean) / sqrt(var + eps) * w of the float32 row x[rows[r]] (x[r] without ``rows``): a weighted layer
+    norm without a shift, the variance taken about the mean."""
+    _need(x, "x", torch.float32); _need(w, "w", torch.float32); _need(out, "out")
+    n, d = out.shape
+    if x.shape[1] != d or w.numel() != d:
+        raise KernelError("layernorm_rows: shape mismatch")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n:
+            raise KernelError("layernorm_rows: rows/out mismatch")
+    elif x.shape[0] != n:
+        raise KernelError("layernorm_rows: x/out mismatch")
+    if n > MAX_STEP_ROWS:
+        raise KernelError("layernorm_rows: too many rows")
+    _run("layernorm_rows", load_library("rowwise").kp_layernorm_rows, _ptr(x), _ptr(w), _ptr(out), _ptr(rows), n, d,
+         ctypes.c_float(eps), dtype_code(out.dtype), STREAM)
+    return out
+
+
+GATE_ACTS = {"silu": 0, "sigmoid": 1}
+
+
+def group_norm_gate_rows(o: torch.Tensor, w: Optional[torch.Tensor], g: torch.Tensor, eps: float, out: torch.Tensor,
+                         groups: int, gate_first: bool, gate_act: str = "silu") -> torch.Tensor:
+    """The float32 rows ``o`` [n, c] RMS-normed in ``groups`` stretches of equal width (a mean square a stretch), with a
+    gate ``act(g)`` (silu or sigmoid; ``g`` [n, c] in the storage type, rows may be strided) and an optional weight
+    ``w`` [c]: ``gate_first`` -> ``norm(o * act(g)) * w``, else ``norm(o) * w * act(g)``."""
+    _need(o, "o", torch.float32); _need(out, "out"); _need(g, "g", out.dtype, contiguous=False)
+    n, c = o.shape
+    if tuple(out.shape) != (n, c) or tuple(g.shape) != (n, c) or groups < 1 or c % groups:
+        raise KernelError("group_norm_gate_rows: shape mismatch")
+    if w is not None:
+        _need(w, "w", torch.float32)
+        if w.numel() != c:
+            raise KernelError("group_norm_gate_rows: weight size")
+    if gate_act not in GATE_ACTS:
+        raise KernelError(f"group_norm_gate_rows: gate '{gate_act}' (silu or sigmoid)")
+    if n > MAX_STEP_ROWS:
+        raise KernelError("group_norm_gate_rows: too many rows")
+    _run("group_norm_gate_rows", load_library("rowwise").kp_group_norm_gate_rows, _ptr(o), c, _ptr(w), _ptr(g), _rows_2d(g, "g"),
+         _ptr(out), c, n, int(groups), c // int(groups), ctypes.c_float(eps), int(bool(gate_first)), GATE_ACTS[gate_act],
+         dtype_code(out.dtype), STREAM)
+    return out
+
+
+def head_gate(o: torch.Tensor, g: torch.Tensor, H: int, hd: int) -> torch.Tensor:
+    """o[r, h hd + i] *= sigmoid(g[r, h]) in place: one gate a head (``g`` [n, H], rows may be strided)."""
+    _need(o, "o"); _need(g, "g", o.dtype, contiguous=False)
+    n = o.shape[0]
+    if tuple(o.shape) != (n, H * hd) or tuple(g.shape) != (n, H):
+        raise KernelError("head_gate: shape mismatch")
+    _run("head_gate", load_library("rowwise").kp_head_gate, _ptr(o), H * hd, _ptr(g), _rows_2d(g, "g"), n, H, hd,
+         dtype_code(o.dtype), STREAM)
+    return o
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _need(x, "x", torch.float32)
+    if not cap > 0:
+        raise KernelError("softcap: the cap must be positive")
+    _run("softcap", load_library("rowwise").kp_softcap, _ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), STREAM)
+    return x
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> torch.Tensor:
+    """out = g sigmoid(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit), rows [gate | up]."""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    n, ff = out.shape
+    if gate_up.shape != (n, 2 * ff):
+        raise KernelError("glu_clamped: shape mismatch")
+    _run("glu_clamped", load_library("rowwise").kp_glu_clamped, _ptr(gate_up), _ptr(out), n, ff, ctypes.c_float(limit),
+         ctypes.c_float(alpha), ctypes.c_float(shift), dtype_code(out.dtype), STREAM)
+    return out
+
+
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}     # codes of the gated units' activations (csrc/common.cuh)
 
 
@@ -534,11 +612,13 @@ LIGHTNING_MAX_DIM = 256    # key rows of a head's state that the scan keeps in r
 def lightning_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_hi: torch.Tensor, decay_lo: torch.Tensor,
                    state: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor,
                    out: torch.Tensor, n_seg: int, H: int, dim: int, vdim: int, activation: Optional[str] = "silu",
-                   write_state: bool = True) -> torch.Tensor:
+                   write_state: bool = True, rotary=None, k_scale: float = 1.0) -> torch.Tensor:
     """``S <- a_h S + k v^T; o = S^T q`` row after row of every segment, from the state in the segment's slot (zero at
     position 0) and back into it.  q, k (H heads of ``dim``) and v (H heads of ``vdim``) are columns of ``qkv`` in
     the storage type with ``activation`` (silu or None) applied here; ``out`` float32 [n, H vdim];
-    ``state`` float32 [slots, H, dim, vdim]; the decays as float32 pairs hi + lo [H]."""
+    ``state`` float32 [slots, H, dim, vdim]; the decays as float32 pairs hi + lo [H].  ``rotary`` = (cos, sin,
+    rotated dimensions): q and k are rotated by position as they are read (dimension i paired with i + half; tables
+    float32 [positions, half]); ``k_scale`` multiplies k behind the rotation."""
     _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)
     _need(decay_hi, "decay_hi", torch.float32); _need(decay_lo, "decay_lo", torch.float32)
     for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
@@ -551,11 +631,26 @@ def lightning_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_
         raise KernelError("lightning_scan: activation is silu or none")
     if dim > LIGHTNING_MAX_DIM:
         raise KernelError(f"lightning_scan: dim={dim} exceeds {LIGHTNING_MAX_DIM}")
+    cos, sin, rot = _lightning_rotary(rotary, dim, "lightning_scan")
     _run("lightning_scan", load_library("lightning").kp_lightning_scan, _ptr(qkv), _rows_2d(qkv, "qkv"), int(q_col), int(k_col),
          int(v_col), _ptr(decay_hi), _ptr(decay_lo), _ptr(state), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(out),
          _rows_2d(out, "out"), int(n_seg), H, dim, vdim, 0 if activation == "silu" else 1, int(bool(write_state)),
-         dtype_code(qkv.dtype), STREAM, work=(4 * n * H * dim * vdim, 0))
+         _ptr(cos), _ptr(sin), rot, ctypes.c_float(k_scale), dtype_code(qkv.dtype), STREAM, work=(4 * n * H * dim * vdim, 0))
     return out
+
+
+def _lightning_rotary(rotary, dim: int, what: str):
+    """(cos, sin, rotated dimensions) checked; (None, None, 0) for no rotation."""
+    if rotary is None:
+        return None, None, 0
+    cos, sin, rot = rotary
+    if cos is None or not rot:
+        return None, None, 0
+    _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32)
+    rot = int(rot)
+    if rot < 2 or rot % 2 or rot > dim or cos.dim() != 2 or cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+        raise KernelError(f"{what}: rotation of {rot} dimensions does not go with heads of {dim} and tables {tuple(cos.shape)}")
+    return cos, sin, rot
 
 
 LIGHTNING_CHUNK_MAX_DIM = 128    # key rows of a head that the chunked form holds in shared memory
@@ -569,13 +664,15 @@ def lightning_chunk_rows() -> int:
 def lightning_chunks(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_pow: torch.Tensor, state: torch.Tensor,
                      cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor, chunk_seg: torch.Tensor,
                      chunk_row0: torch.Tensor, seg_chunk0: torch.Tensor, n_chunks: int, out: torch.Tensor, n_seg: int,
-                     H: int, dim: int, vdim: int, activation: Optional[str] = "silu", write_state: bool = True) -> torch.Tensor:
+                     H: int, dim: int, vdim: int, activation: Optional[str] = "silu", write_state: bool = True,
+                     rotary=None, k_scale: float = 1.0) -> torch.Tensor:
     """The recurrence of :func:`lightning_scan` for segments of many rows: chunks of rows as small matrix products
     (float32 on the CUDA cores), the chunks of all segments side by side: every chunk's own sum, a short serial pass
     over a segment's chunks for the states at their heads, every chunk's outputs.  ``decay_pow``: float32
     [H, rows + 1], the powers ``a_h^m`` (made in double).  Sums have another order than the scan's.  ``chunk_seg`` /
     ``chunk_row0`` [n_chunks]: a chunk's segment and first row (chunks of at most :func:`lightning_chunk_rows` rows,
-    a segment's chunks in order); ``seg_chunk0`` [n_seg + 1]: the first chunk of every segment."""
+    a segment's chunks in order); ``seg_chunk0`` [n_seg + 1]: the first chunk of every segment.  ``rotary`` and
+    ``k_scale`` as in :func:`lightning_scan`."""
     _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)
     _need(decay_pow, "decay_pow", torch.float32)
     for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot"), (chunk_seg, "chunk_seg"),
@@ -591,14 +688,110 @@ def lightning_chunks(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, deca
         raise KernelError("lightning_chunks: activation is silu or none")
     if dim > LIGHTNING_CHUNK_MAX_DIM:
         raise KernelError(f"lightning_chunks: dim={dim} exceeds {LIGHTNING_CHUNK_MAX_DIM}")
+    cos, sin, rot = _lightning_rotary(rotary, dim, "lightning_chunks")
     scratch = torch.empty(n_chunks * H * dim * vdim, dtype=torch.float32, device=qkv.device)
     _run("lightning_chunks", load_library("lightning").kp_lightning_chunks, _ptr(qkv), _rows_2d(qkv, "qkv"), int(q_col),
          int(k_col), int(v_col), _ptr(decay_pow), _ptr(state), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(chunk_seg),
          _ptr(chunk_row0), _ptr(seg_chunk0), int(n_chunks), _ptr(scratch), _ptr(out), _rows_2d(out, "out"), int(n_seg), H, dim,
-         vdim, 0 if activation == "silu" else 1, int(bool(write_state)), dtype_code(qkv.dtype), STREAM,
-         work=(4 * n * H * dim * vdim, 0))
+         vdim, 0 if activation == "silu" else 1, int(bool(write_state)), _ptr(cos), _ptr(sin), rot, ctypes.c_float(k_scale),
+         dtype_code(qkv.dtype), STREAM, work=(4 * n * H * dim * vdim, 0))
     LAUNCHES[0] += 2
     return out
+
+
+# ------------------------------------------------------------------ selective state space (mamba2)
+
+SSM_MAX_STATE = 256        # rows of a head's state that the scan keeps in registers
+SSM_CHUNK_MAX_STATE = 128  # rows of a head's state that the chunked form holds in shared memory
+SSM_MAX_TAPS = 16
+
+
+def ssm_conv(p: torch.Tensor, conv_col: int, dt_col: int, taps: torch.Tensor, bias: torch.Tensor, dt_bias: torch.Tensor,
+             a_log: torch.Tensor, kept: torch.Tensor, row_seg: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor,
+             seg_slot: torch.Tensor, out: torch.Tensor, dt_out: torch.Tensor, da_out: torch.Tensor, n_seg: int,
+             single_rows: bool, keep: bool = True) -> None:
+    """``out = silu(conv(p[:, conv_col : conv_col + C]) + bias)`` (a causal convolution a channel, taps [C, K], the
+    last tap on the current row; rows before a segment come from the request's kept inputs, zero at position 0),
+    ``dt_out = softplus(p[:, dt_col : dt_col + H] + dt_bias)`` and ``da_out = -exp(a_log) * dt_out`` (float32).
+    ``kept``: float32 [slots, stride] whose rows begin with the last K - 1 inputs as [K - 1, C]; renewed unless
+    ``keep`` is False (``single_rows``: every segment has one row, and one launch does both)."""
+    _need(p, "p", contiguous=False); _need(out, "out", p.dtype); _need(kept, "kept", torch.float32, contiguous=False)
+    for t, nm in ((taps, "taps"), (bias, "bias"), (dt_bias, "dt_bias"), (a_log, "a_log"), (dt_out, "dt_out"), (da_out, "da_out")):
+        _need(t, nm, torch.float32)
+    for t, nm in ((row_seg, "row_seg"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
+        _need(t, nm, torch.int32)
+    n, C = out.shape
+    H, K = dt_bias.numel(), taps.shape[1]
+    if (p.shape[0] != n or tuple(taps.shape) != (C, K) or bias.numel() != C or a_log.numel() != H or tuple(dt_out.shape) != (n, H)
+            or tuple(da_out.shape) != (n, H) or conv_col + C > p.shape[1] or dt_col + H > p.shape[1] or kept.dim() != 2
+            or kept.stride(1) != 1 or kept.shape[1] < (K - 1) * C):
+        raise KernelError("ssm_conv: shape mismatch")
+    if K > SSM_MAX_TAPS:
+        raise KernelError(f"ssm_conv: {K} taps exceed {SSM_MAX_TAPS}")
+    _run("ssm_conv", load_library("ssm").kp_ssm_conv, _ptr(p), _rows_2d(p, "p"), int(conv_col), int(dt_col), _ptr(taps), _ptr(bias),
+         _ptr(dt_bias), _ptr(a_log), _ptr(kept), ctypes.c_longlong(kept.stride(0)), _ptr(row_seg), _ptr(cu_rows), _ptr(seg_pos),
+         _ptr(seg_slot), _ptr(out), _ptr(dt_out), _ptr(da_out), n, int(n_seg), C, H, K, int(bool(single_rows)), int(bool(keep)),
+         dtype_code(p.dtype), STREAM)
+    if keep and not single_rows and K > 1:
+        LAUNCHES[0] += 1
+
+
+def _ssm_check(what, xbc, dt, da, D, state, y, H, G, N, P):
+    _need(xbc, "xbc", contiguous=False); _need(y, "y", torch.float32); _need(state, "state", torch.float32, contiguous=False)
+    for t, nm in ((dt, "dt"), (da, "da"), (D, "D")):
+        _need(t, nm, torch.float32)
+    n = xbc.shape[0]
+    if (tuple(y.shape) != (n, H * P) or tuple(dt.shape) != (n, H) or tuple(da.shape) != (n, H) or D.numel() != H or H % G
+            or xbc.shape[1] < H * P + 2 * G * N or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * N * P):
+        raise KernelError(f"{what}: shape mismatch")
+    return n
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, da: torch.Tensor, D: torch.Tensor, state: torch.Tensor, cu_rows: torch.Tensor,
+             seg_pos: torch.Tensor, seg_slot: torch.Tensor, y: torch.Tensor, n_seg: int, H: int, G: int, N: int, P: int,
+             write_state: bool = True) -> torch.Tensor:
+    """``S <- exp(da) S + dt B x^T; y = S^T C + D x`` row after row of every segment, from the state in the segment's
+    slot (zero at position 0) and back into it.  ``xbc`` rows hold [x: H heads of P | B: G groups of N | C: the same]
+    in the storage type; ``dt``, ``da`` float32 [n, H]; ``state`` float32 [slots, stride] whose rows begin with
+    [H, N, P]; ``y`` float32 [n, H P]."""
+    n = _ssm_check("ssm_scan", xbc, dt, da, D, state, y, H, G, N, P)
+    for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
+        _need(t, nm, torch.int32)
+    if N > SSM_MAX_STATE:
+        raise KernelError(f"ssm_scan: state={N} exceeds {SSM_MAX_STATE}")
+    _run("ssm_scan", load_library("ssm").kp_ssm_scan, _ptr(xbc), _rows_2d(xbc, "xbc"), H * P, H * P + G * N, _ptr(dt), _ptr(da),
+         _ptr(D), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(y),
+         _rows_2d(y, "y"), int(n_seg), H, G, N, P, int(bool(write_state)), dtype_code(xbc.dtype), STREAM,
+         work=(4 * n * H * N * P, 0))
+    return y
+
+
+def ssm_chunk_rows() -> int:
+    return int(load_library("ssm").kp_ssm_chunk_rows())
+
+
+def ssm_chunks(xbc: torch.Tensor, dt: torch.Tensor, da: torch.Tensor, D: torch.Tensor, state: torch.Tensor, cu_rows: torch.Tensor,
+               seg_pos: torch.Tensor, seg_slot: torch.Tensor, chunk_seg: torch.Tensor, chunk_row0: torch.Tensor,
+               seg_chunk0: torch.Tensor, n_chunks: int, y: torch.Tensor, n_seg: int, H: int, G: int, N: int, P: int,
+               write_state: bool = True) -> torch.Tensor:
+    """The recurrence of :func:`ssm_scan` for segments of many rows, chunks of rows as small float32 matrix products,
+    the chunks of all segments side by side (sums, a serial pass over a segment's chunks, outputs).  The chunk lists
+    as in :func:`lightning_chunks`.  Sums have another order than the scan's."""
+    n = _ssm_check("ssm_chunks", xbc, dt, da, D, state, y, H, G, N, P)
+    for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot"), (chunk_seg, "chunk_seg"),
+                  (chunk_row0, "chunk_row0"), (seg_chunk0, "seg_chunk0")):
+        _need(t, nm, torch.int32)
+    if chunk_seg.numel() < n_chunks or chunk_row0.numel() < n_chunks or seg_chunk0.numel() < n_seg + 1:
+        raise KernelError("ssm_chunks: chunk lists too short")
+    if N > SSM_CHUNK_MAX_STATE:
+        raise KernelError(f"ssm_chunks: state={N} exceeds {SSM_CHUNK_MAX_STATE}")
+    scratch = torch.empty(n_chunks * H * (N * P + 1), dtype=torch.float32, device=xbc.device)
+    _run("ssm_chunks", load_library("ssm").kp_ssm_chunks, _ptr(xbc), _rows_2d(xbc, "xbc"), H * P, H * P + G * N, _ptr(dt), _ptr(da),
+         _ptr(D), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(chunk_seg),
+         _ptr(chunk_row0), _ptr(seg_chunk0), int(n_chunks), _ptr(scratch), _ptr(y), _rows_2d(y, "y"), int(n_seg), H, G, N, P,
+         int(bool(write_state)), dtype_code(xbc.dtype), STREAM, work=(4 * n * H * N * P, 0))
+    LAUNCHES[0] += 2
+    return y
 
 
 # ------------------------------------------------------------------ attention
@@ -649,6 +842,33 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
                                   _ptr(slot_map), _ptr(q_out), 0 if q_out is None else _rows_2d(q_out, "q_out"), _ptr(cache),
                                   page_size,
                                   n, H, G, hd, int(write_kv), int(v_col), dtype_code(qkv.dtype), STREAM)
+    return q_out
+
+
+def qk_rownorm_kv(qkv: torch.Tensor, k_col: int, v_col: int, q_w: torch.Tensor, k_w: Optional[torch.Tensor], eps: float,
+                  count_q: int, count_k: int, slot_map: Optional[torch.Tensor], q_out: torch.Tensor,
+                  cache: Optional[torch.Tensor], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+    """RMS norm of q and of k each over its whole projection (all heads at once, weights as long as the projections),
+    no rotation; q to ``q_out``, and with ``cache`` given the normed k and v to their pages.  Rows hold q at column
+    0 (H heads stored ``hd`` wide), k at ``k_col`` and v at ``v_col`` (G heads each).  ``count_q`` / ``count_k``: the
+    numbers the means are taken over (smaller than H hd and G hd where heads are stored wider than they are, with
+    zeros behind)."""
+    _need(qkv, "qkv", contiguous=False); _need(q_out, "q_out", qkv.dtype); _need(q_w, "q_w", torch.float32)
+    n = qkv.shape[0]
+    if tuple(q_out.shape) != (n, H * hd) or q_w.numel() != H * hd or H * hd > qkv.shape[1]:
+        raise KernelError("qk_rownorm_kv: shape mismatch")
+    write_kv = cache is not None
+    if write_kv:
+        _need(cache, "cache", qkv.dtype); _need(slot_map, "slot_map", torch.int32); _need(k_w, "k_w", torch.float32)
+        if (tuple(cache.shape[1:]) != (2, G, page_size, hd) or k_w.numel() != G * hd
+                or max(k_col, v_col) + G * hd > qkv.shape[1] or min(k_col, v_col) < H * hd):
+            raise KernelError(f"qk_rownorm_kv: cache layout {tuple(cache.shape)} or columns")
+    if n > MAX_STEP_ROWS:
+        raise KernelError("qk_rownorm_kv: too many rows")
+    _run("qk_rownorm_kv", load_library("qkrope").kp_qk_rownorm_kv, _ptr(qkv), _rows_2d(qkv, "qkv"), int(k_col), int(v_col),
+         _ptr(q_w), _ptr(k_w if write_kv else None), ctypes.c_float(eps), ctypes.c_float(count_q), ctypes.c_float(count_k),
+         _ptr(slot_map if write_kv else None), _ptr(q_out), H * hd, _ptr(cache), page_size, n, H, G, hd, int(write_kv),
+         dtype_code(qkv.dtype), STREAM)
     return q_out
 
 

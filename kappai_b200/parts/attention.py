@@ -22,9 +22,23 @@ always do; the ``mma.sync`` kernels then take them as three bfloat16 parts, and
 the tcgen05 prompt kernel, which rounds them to one bfloat16 operand, is left
 out); the default ``"operand"`` rounds them to bfloat16 as a matrix operand.
 
+More variants: ``qk_norm`` = ``"projection"`` norms q, and k, each as one row
+over all its heads at once, with weights as long as the projections (the
+default ``"per_head"`` is the norm above); ``gate`` = ``"head_sigmoid"`` is a
+gate of one number a head, ``sigmoid(h Wg^T)`` with Wg [num_heads, hidden];
+``value_dim`` (default head_dim) is the width of a value head: where it differs
+from head_dim a cache head is as wide as the wider of the two rounded up to a
+multiple of 16, and the matrices get zero rows or columns for that at load;
+``kv`` = ``"borrowed"``: the mixer has no key and value tensors and writes no
+cache: its schedule entry names the entry whose cache its queries read (after
+that entry's key norm).  ``cache_window``: how many positions back the cache
+must keep keys (at least ``window``; larger where a borrower's window is).
+
 Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
-scale, qk_norm_eps (None: no q/k norm), window (None: all keys), block (None),
-values ("projection" | "keys"), gate (None | "sigmoid"), softmax_weights ("operand" | "float32"), position (a
+value_dim, scale, qk_norm_eps (None: no q/k norm), qk_norm ("per_head" |
+"projection"), window (None: all keys), cache_window, block (None), values
+("projection" | "keys"), kv ("own" | "borrowed"), gate (None | "sigmoid" |
+"head_sigmoid"), softmax_weights ("operand" | "float32"), position (a
 ``position`` PartSpec), bias.
 """
 from __future__ import annotations
@@ -181,19 +195,46 @@ class Attention(PagedAttentionKernels, Part):
             raise ConfigError(f"attention: values='{values}' (expected 'projection' or 'keys')")
         self.values_are_keys = values == "keys"
         gate = self._p("gate", None)
-        if gate not in (None, "sigmoid"):
-            raise ConfigError(f"attention: gate='{gate}' (expected 'sigmoid' or none)")
+        if gate not in (None, "sigmoid", "head_sigmoid"):
+            raise ConfigError(f"attention: gate='{gate}' (expected 'sigmoid', 'head_sigmoid' or none)")
         self.gated = gate is not None
+        self.head_gate = gate == "head_sigmoid"
         sw = self._p("softmax_weights", "operand")
         if sw not in ("operand", "float32"):
             raise ConfigError(f"attention: softmax_weights='{sw}' (expected 'operand' or 'float32')")
         self.exact_weights = sw == "float32"
+        self.qk_norm = self._p("qk_norm", "per_head")
+        if self.qk_norm not in ("per_head", "projection"):
+            raise ConfigError(f"attention: qk_norm='{self.qk_norm}' (expected 'per_head' or 'projection')")
+        kv = self._p("kv", "own")
+        if kv not in ("own", "borrowed"):
+            raise ConfigError(f"attention: kv='{kv}' (expected 'own' or 'borrowed')")
+        self.borrows = kv == "borrowed"
+        cw = self._p("cache_window", self.window)
+        self.cache_window: Optional[int] = None if cw is None else int(cw)
+        if self.window is not None and self.cache_window is not None and self.cache_window < int(self.window):
+            raise ConfigError(f"attention: cache_window={self.cache_window} is smaller than window={self.window}")
         if self.bias and (self.values_are_keys or self.gated):
             raise ConfigError("attention: biases are not combined with values='keys' or a gate")
         if self.H < 1 or self.G < 1 or self.H % self.G:
             raise ConfigError(f"attention: num_heads={self.H} must be a multiple of num_kv_heads={self.G}")
+        # dim, vdim: the heads as the model has them; hd: as the cache and the kernels see them
+        self.dim = self.hd
+        self.vdim = int(self._p("value_dim", self.dim))
+        if self.qk_norm == "projection" or self.vdim != self.dim:
+            if self.qk_norm_eps is not None and self.qk_norm != "projection":
+                raise ConfigError("attention: value_dim differs from head_dim, which the per-head q/k norm does not take")
+            if self.values_are_keys or self.bias:
+                raise ConfigError("attention: values='keys' and biases want value_dim = head_dim and the per-head norm")
+            if min(self.dim, self.vdim) < 1:
+                raise ConfigError("attention: head sizes must be positive")
+            self.hd = -(-max(self.dim, self.vdim) // 16) * 16
+        if self.borrows and (self.values_are_keys or self.bias or self.qk_norm != "projection"):
+            raise ConfigError("attention: kv='borrowed' goes with qk_norm='projection', a value matrix elsewhere and no biases")
+        if self.qk_norm == "projection" and self.qk_norm_eps is None:
+            raise ConfigError("attention: qk_norm='projection' needs qk_norm_eps")
         if self.hd % 2 or not (2 <= self.hd <= 256):
-            raise ConfigError(f"attention: head_dim={self.hd} is not supported by the kernels "
+            raise ConfigError(f"attention: head_dim={self.dim} is not supported by the kernels "
                               "(an even number from 2 to 256)")
         pos = self._p("position", None)
         if pos is None:
@@ -204,46 +245,74 @@ class Attention(PagedAttentionKernels, Part):
         self.graph_safe = bool(self.position.graph_safe)     # a position part that reads host values keeps it eager
         if self.values_are_keys and not hasattr(self.position, "fused_rotary"):
             raise ConfigError("attention: values='keys' needs a position encoding that runs in the fused q/k kernel")
+        if self.qk_norm == "projection" and (not hasattr(self.position, "fused_rotary") or self.position.fused_rotary()[2]):
+            raise ConfigError("attention: qk_norm='projection' runs without a rotation")
         self._tile_setup()
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        d, H, G, hd = self.d, self.H, self.G, self.hd
-        s = {"q_proj.weight": WeightSpec((H * hd, d)), "k_proj.weight": WeightSpec((G * hd, d)),
-             "out_proj.weight": WeightSpec((d, H * hd))}
-        if not self.values_are_keys:
-            s["v_proj.weight"] = WeightSpec((G * hd, d))
+        d, H, G = self.d, self.H, self.G
+        s = {"q_proj.weight": WeightSpec((H * self.dim, d)), "out_proj.weight": WeightSpec((d, H * self.vdim))}
+        if not self.borrows:
+            s["k_proj.weight"] = WeightSpec((G * self.dim, d))
+            if not self.values_are_keys:
+                s["v_proj.weight"] = WeightSpec((G * self.vdim, d))
         if self.gated:
-            s["gate_proj.weight"] = WeightSpec((H * hd, d))
-        if self.qk_norm_eps is not None:
-            s["q_norm.weight"] = WeightSpec((hd,), "norm")
-            s["k_norm.weight"] = WeightSpec((hd,), "norm")
+            s["gate_proj.weight"] = WeightSpec((H if self.head_gate else H * self.vdim, d))
+        if self.qk_norm == "projection":
+            s["q_norm.weight"] = WeightSpec((H * self.dim,), "norm")
+            if not self.borrows:
+                s["k_norm.weight"] = WeightSpec((G * self.dim,), "norm")
+        elif self.qk_norm_eps is not None:
+            s["q_norm.weight"] = WeightSpec((self.dim,), "norm")
+            s["k_norm.weight"] = WeightSpec((self.dim,), "norm")
         if self.bias:
             for n, sz in (("q_proj", H * hd), ("k_proj", G * hd), ("v_proj", G * hd), ("out_proj", d)):
                 s[n + ".bias"] = WeightSpec((sz,), "bias")
         return s
 
+    def _pad_heads(self, w, heads, width):
+        """[heads width, ...] -> [heads hd, ...]: every head's rows, then zero rows up to the cache head's width."""
+        if width == self.hd:
+            return w.contiguous()
+        out = torch.zeros((heads, self.hd) + tuple(w.shape[1:]), dtype=w.dtype, device=w.device)
+        out[:, :width] = w.reshape((heads, width) + tuple(w.shape[1:]))
+        return out.reshape((heads * self.hd,) + tuple(w.shape[1:]))
+
     def bind(self, w):
         # one product for everything that reads the layer's input: rows [q | k | v (if it has a matrix) | gate]
-        rows = [w["q_proj.weight"], w["k_proj.weight"]]
-        if not self.values_are_keys:
-            rows.append(w["v_proj.weight"])
+        H, G, hd = self.H, self.G, self.hd
+        rows = [self._pad_heads(w["q_proj.weight"], H, self.dim)]
+        if not self.borrows:
+            rows.append(self._pad_heads(w["k_proj.weight"], G, self.dim))
+            if not self.values_are_keys:
+                rows.append(self._pad_heads(w["v_proj.weight"], G, self.vdim))
         self.gate_col = sum(r.shape[0] for r in rows)
         if self.gated:
-            rows.append(w["gate_proj.weight"])
+            rows.append(w["gate_proj.weight"] if self.head_gate else self._pad_heads(w["gate_proj.weight"], H, self.vdim))
+        n_rows = sum(r.shape[0] for r in rows)
+        if n_rows % 8:
+            # zero rows behind the last, so that a row of the product's output starts on a 16-byte boundary
+            rows.append(torch.zeros((8 - n_rows % 8, self.d), dtype=rows[0].dtype, device=rows[0].device))
         self.w_qkv = torch.cat(rows, 0).contiguous()
-        self.v_col = self.H * self.hd if self.values_are_keys else (self.H + self.G) * self.hd
-        self.w_o = w["out_proj.weight"].contiguous()
+        self.k_col = H * hd
+        self.v_col = H * hd if self.values_are_keys else (H + G) * hd
+        self.w_o = self._pad_heads(w["out_proj.weight"].t().contiguous(), H, self.vdim).t().contiguous()
         self.b_qkv = self.b_o = None
         if self.bias:
             self.b_qkv = torch.cat([w[n + ".bias"].float() for n in ("q_proj", "k_proj", "v_proj")]).contiguous()
             self.b_o = w["out_proj.bias"].float().contiguous()
         self.q_w = self.k_w = None
-        if self.qk_norm_eps is not None:
+        if self.qk_norm == "projection":
+            self.q_w = self._pad_heads(w["q_norm.weight"].float(), H, self.dim)
+            if not self.borrows:
+                self.k_w = self._pad_heads(w["k_norm.weight"].float(), G, self.dim)
+        elif self.qk_norm_eps is not None:
             self.q_w = w["q_norm.weight"].float().contiguous()
             self.k_w = w["k_norm.weight"].float().contiguous()
 
     def cache_spec(self):
-        return PagedKVSpec(self.G, self.hd, self.window, None if self.block is None else int(self.block))
+        # (a borrower names what it reads, so that the engine can see that lender and borrower agree)
+        return PagedKVSpec(self.G, self.hd, self.cache_window, None if self.block is None else int(self.block))
 
     def forward(self, h, residual, ctx, cache):
         """``cache``: a :class:`~kappai_b200.cache.storage.KVLayerView`."""
@@ -252,7 +321,12 @@ class Attention(PagedAttentionKernels, Part):
         qkv = linear(h, self.w_qkv, self.b_qkv)
         q = torch.empty((ctx.n_rows, H * hd), dtype=qkv.dtype, device=qkv.device)
         kv_out = cache.tensor if cache.writes else None
-        if hasattr(self.position, "fused_rotary"):
+        if self.borrows and cache.writes:
+            raise ValueError("attention: a mixer with kv='borrowed' was given a cache of its own")
+        if self.qk_norm == "projection":
+            K.qk_rownorm_kv(qkv, self.k_col, self.v_col, self.q_w, self.k_w, self.qk_norm_eps, H * self.dim, G * self.dim,
+                            view.slot_map, q, kv_out, view.page_size, H, G, hd)
+        elif hasattr(self.position, "fused_rotary"):
             cos, sin, rot, inter = self.position.fused_rotary()
             K.qk_norm_rope_kv(qkv, self.q_w, self.k_w, self.qk_norm_eps or 0.0, cos, sin, rot, inter,
                               ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd, self.v_col)
@@ -265,7 +339,9 @@ class Attention(PagedAttentionKernels, Part):
             K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q, kv_out,
                               view.page_size, H, G, hd)
         o = self._attend(q, ctx, view, cache)
-        if self.gated:
+        if self.head_gate:
+            K.head_gate(o, qkv[:, self.gate_col:self.gate_col + H], H, hd)
+        elif self.gated:
             K.sigmoid_gate(o, qkv[:, self.gate_col:self.gate_col + H * hd])
         linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
 

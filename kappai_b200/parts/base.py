@@ -138,4 +138,4 @@ def _ensure_builtin() -> None:
     global _builtin
     if not _builtin:
         _builtin = True
-        from . import norm, position, attention, shortconv, lightning, ffn, block, embedding, side  # noqa: F401
+        from . import norm, position, attention, shortconv, lightning, ssm, ffn, block, embedding, side  # noqa: F401

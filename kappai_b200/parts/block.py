@@ -12,6 +12,11 @@ without a feed-forward has the first half only.  The sum and the norm are
 float32; one kernel norms a sum and writes what the next sublayer needs (its
 input in the compute type and ``alpha`` times the new residual to add into), so
 a layer costs two row-wise launches, as a pre-norm layer does.
+
+``parallel_residual``: ``h = norm1(x); x += mixer(h); x += ffn(h)``: one norm a
+layer, and both sublayers read its output.  Each sublayer adds its float32
+output into the float32 residual, so the layer's sum is
+``(x + mixer(h)) + ffn(h)``.
 """
 from __future__ import annotations
 
@@ -87,5 +92,30 @@ class PostNormResidualBlock(Part):
         ctx.postnorm_carry = (x, self.alpha, x if f32 else h2, acc)
 
 
+class ParallelResidualBlock(Part):
+    category = "block"
+    graph_safe = True
+
+    def assemble(self, mixer, ffn, mixer_norm, ffn_norm, side=None):
+        if ffn_norm is not None:
+            raise ValueError("parallel_residual: the sublayers share one norm")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm, self.side = mixer, ffn, mixer_norm, None, side
+        return self
+
+    def forward(self, x, ctx, cache):
+        if self.mixer_norm is not None:
+            h = self.mixer_norm.forward(x)
+        elif self.env.dtype == torch.float32:
+            h = x.clone()                      # the sublayers add into x while the second still has to read its input
+        else:
+            h = K.cast(x, torch.empty(x.shape, dtype=self.env.dtype, device=x.device))
+        self.mixer.forward(h, x, ctx, cache)
+        if self.ffn is not None:
+            self.ffn.forward(h, x, ctx)
+        if self.side is not None:
+            self.side.forward(x, ctx)
+
+
 register_part("block", "prenorm_residual", PreNormResidualBlock)
+register_part("block", "parallel_residual", ParallelResidualBlock)
 register_part("block", "postnorm_residual", PostNormResidualBlock)

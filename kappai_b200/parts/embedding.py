@@ -5,7 +5,9 @@ src/recipe/scratch.c:195-235), into the float32 residual.  With ``positions``
 (a number of positions) the embedding also owns a table of learned position
 vectors and adds the row of the token's position, unscaled.  The head computes
 ``logits = h W^T`` in float32 output (times ``scale`` if the architecture has
-one); when tied, W is the embedding table (src/model.c:2562-2572).
+one); when tied, W is the embedding table (src/model.c:2562-2572).  With
+``softcap`` (a positive number c) the logits are then bounded smoothly:
+``logits <- c tanh(logits / c)``.
 
 ``token_table``: a second table by token id that other parts read columns of
 (a per-layer token input); it has no forward of its own.
@@ -83,6 +85,10 @@ class LMHead(Part):
         self.tied = bool(self._p("tied", True))
         s = self._p("scale", None)
         self.scale = 1.0 if s is None else float(s)
+        c = self._p("softcap", None)
+        self.softcap = None if c is None else float(c)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"lm_head: softcap={self.softcap} must be positive")
         self.weight = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -99,6 +105,8 @@ class LMHead(Part):
         logits = linear(h, self.weight, out_dtype=torch.float32)
         if self.scale != 1.0:
             K.scale_cast(logits, None, logits, self.scale)
+        if self.softcap is not None:
+            K.softcap(logits, self.softcap)
         return logits
 
 

@@ -9,6 +9,12 @@ Params: hidden_size, intermediate_size, bias, activation (``silu`` by default;
 ``relu`` and ``gelu_tanh`` make the same unit with another function on the gate:
 kind ``glu``).
 
+``glu_clamped``: the same three matrices with another unit between them: the
+gate is bounded above and the other branch on both sides,
+``g = min(h Wg^T + bg, limit)``, ``u = clamp(h Wu^T + bu, -limit, limit)``,
+``f = (g sigmoid(alpha g) (u + shift)) Wd^T + bd``.  Params: hidden_size,
+intermediate_size, limit, alpha, shift, bias.
+
 ``moe``: a mixture of ``num_experts`` such units without biases, of which every
 row uses the ``top`` with the largest router logits ``z = h Wr^T + b`` (float32),
 weighted by the softmax over those ``top`` logits alone; see csrc/moe.cu.
@@ -66,6 +72,28 @@ class SwiGLU(Part):
 
     def forward(self, h, residual, ctx):
         act = linear_swiglu(h, self.w_gu, self.b_gu, self.activation)
+        linear(act, self.w_down, self.b_down, out=residual, accumulate=True)
+
+
+class ClampedGLU(SwiGLU):
+    """``glu_clamped``: see the module's text.  Gate and up run as one product; the unit is computed in float32 from
+    their values in the storage type."""
+
+    def __init__(self, params, env):
+        Part.__init__(self, params, env)
+        self.d = int(self._p("hidden_size"))
+        self.ff = int(self._p("intermediate_size"))
+        self.bias = bool(self._p("bias", False))
+        self.limit = float(self._p("limit"))
+        self.alpha = float(self._p("alpha"))
+        self.shift = float(self._p("shift", 0.0))
+        if not self.limit > 0:
+            raise ConfigError(f"glu_clamped: limit={self.limit} must be positive")
+
+    def forward(self, h, residual, ctx):
+        gu = linear(h, self.w_gu, self.b_gu)
+        act = torch.empty((h.shape[0], self.ff), dtype=h.dtype, device=h.device)
+        K.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
         linear(act, self.w_down, self.b_down, out=residual, accumulate=True)
 
 
@@ -166,4 +194,5 @@ class MixtureOfExperts(Part):
 
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "glu", SwiGLU)
+register_part("feed_forward", "glu_clamped", ClampedGLU)
 register_part("feed_forward", "moe", MixtureOfExperts)

@@ -19,8 +19,16 @@ more runs the chunked kernels (the rows of a chunk as small float32 matrix
 products, the chunks of all segments side by side; the list of chunks is a
 step table built on the host).
 
+Variants, each a parameter ("retention" is this mixer with all four): ``position``
+(a ``position`` PartSpec of kind ``rope``, "rotate half" pairing) rotates q and
+k by position as the kernels read them, in float32; ``k_scale`` multiplies k
+behind the rotation; ``norm`` = ``"per_head"`` divides every head's ``o`` by
+its own root mean square and has no weight (the default ``"all_heads"`` is the
+norm above); ``gate`` = ``"silu"`` multiplies by ``silu(h Wg^T)`` instead.
+
 Params: hidden_size, num_heads, head_dim, value_dim, decay (a list, one a
-head), norm_eps, activation ("silu" | None), gate ("sigmoid").
+head), norm_eps, activation ("silu" | None), gate ("sigmoid" | "silu"), norm
+("all_heads" | "per_head"), position (None | a rope PartSpec), k_scale.
 """
 from __future__ import annotations
 
@@ -30,10 +38,10 @@ import numpy as np
 import torch
 
 from ..cache.spec import StateSpec
-from ..config.schema import ConfigError
+from ..config.schema import ConfigError, PartSpec
 from ..ops import kernels as K
 from ..ops.linear import linear
-from .base import Part, WeightSpec, register_part
+from .base import Part, WeightSpec, make_part, register_part
 
 
 CHUNKED_FROM = 16      # rows of a step's longest segment from which the chunked kernels run (16-bit mode)
@@ -84,8 +92,27 @@ class LightningAttention(Part):
             raise ConfigError("lightning: a decay lies between 0 and 1")
         if self.activation not in ("silu", None):
             raise ConfigError(f"lightning: activation='{self.activation}' (expected 'silu' or none)")
-        if self._p("gate", "sigmoid") != "sigmoid":
-            raise ConfigError("lightning: the output gate is a sigmoid")
+        self.gate = self._p("gate", "sigmoid")
+        if self.gate not in ("sigmoid", "silu"):
+            raise ConfigError(f"lightning: gate='{self.gate}' (expected 'sigmoid' or 'silu')")
+        self.norm = self._p("norm", "all_heads")
+        if self.norm not in ("all_heads", "per_head"):
+            raise ConfigError(f"lightning: norm='{self.norm}' (expected 'all_heads' or 'per_head')")
+        self.k_scale = float(self._p("k_scale", 1.0))
+        pos = self._p("position", None)
+        self.rotary = None
+        if pos is not None:
+            pos = PartSpec(**pos) if isinstance(pos, dict) else pos
+            enc = make_part("position", pos, env)
+            if not hasattr(enc, "fused_rotary"):
+                raise ConfigError("lightning: the position encoding must be one that the kernels apply themselves")
+            cos, sin, rot, interleaved = enc.fused_rotary()
+            if rot:
+                if interleaved:
+                    raise ConfigError("lightning: the kernels rotate pairs (i, i + half) only")
+                if rot > self.dim:
+                    raise ConfigError(f"lightning: rotary_dim={rot} exceeds head_dim={self.dim}")
+                self.rotary = (cos, sin, rot)
         if min(self.H, self.dim, self.vdim) < 1 or self.dim > K.LIGHTNING_MAX_DIM:
             raise ConfigError(f"lightning: head_dim={self.dim} is not supported by the kernels (1 to {K.LIGHTNING_MAX_DIM})")
         self.chunked = env.dtype != torch.float32 and self.dim <= K.LIGHTNING_CHUNK_MAX_DIM and env.device.type == "cuda"
@@ -98,14 +125,17 @@ class LightningAttention(Part):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         d, H = self.d, self.H
-        return {"q_proj.weight": WeightSpec((H * self.dim, d)), "k_proj.weight": WeightSpec((H * self.dim, d)),
-                "v_proj.weight": WeightSpec((H * self.vdim, d)), "gate_proj.weight": WeightSpec((H * self.vdim, d)),
-                "out_proj.weight": WeightSpec((d, H * self.vdim)), "norm.weight": WeightSpec((H * self.vdim,), "norm")}
+        s = {"q_proj.weight": WeightSpec((H * self.dim, d)), "k_proj.weight": WeightSpec((H * self.dim, d)),
+             "v_proj.weight": WeightSpec((H * self.vdim, d)), "gate_proj.weight": WeightSpec((H * self.vdim, d)),
+             "out_proj.weight": WeightSpec((d, H * self.vdim))}
+        if self.norm == "all_heads":
+            s["norm.weight"] = WeightSpec((H * self.vdim,), "norm")
+        return s
 
     def bind(self, w):
         self.w_in = torch.cat([w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"], w["gate_proj.weight"]], 0).contiguous()
         self.w_o = w["out_proj.weight"].contiguous()
-        self.norm_w = w["norm.weight"].float().contiguous()
+        self.norm_w = w["norm.weight"].float().contiguous() if self.norm == "all_heads" else None
         # a decay as a float32 pair: hi the nearest float32, lo what it leaves of the constant
         a = np.asarray(self.decay, dtype=np.float64)
         hi = a.astype(np.float32)
@@ -129,7 +159,8 @@ class LightningAttention(Part):
         o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
         chunks = ctx.tables.get(self.step_tables_key) if self.chunked else None
         scan = lambda n_seg: K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows,
-                                              ctx.seg_pos, ctx.seg_slot, o, n_seg, H, dim, vdim, self.activation, cache.writes)
+                                              ctx.seg_pos, ctx.seg_slot, o, n_seg, H, dim, vdim, self.activation, cache.writes,
+                                              self.rotary, self.k_scale)
         if chunks is not None:
             # (measured at 2,048 rows against the scan: 32 heads of 64 x 64 151 us against 430, of 128 x 128 620 against 1291)
             nl = chunks.n_lead
@@ -137,12 +168,16 @@ class LightningAttention(Part):
                 scan(nl)                                         # decoded tokens beside the portions: the scan takes them
             K.lightning_chunks(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows[nl:], ctx.seg_pos[nl:],
                                ctx.seg_slot[nl:], chunks.chunk_seg, chunks.chunk_row0, chunks.seg_chunk0, chunks.n_chunks, o,
-                               ctx.n_seg - nl, H, dim, vdim, self.activation, cache.writes)
+                               ctx.n_seg - nl, H, dim, vdim, self.activation, cache.writes, self.rotary, self.k_scale)
         else:
             scan(ctx.n_seg)
         g0 = 2 * H * dim + H * vdim
         og = torch.empty((n, H * vdim), dtype=p.dtype, device=p.device)
-        K.norm_gate_rows(o, self.norm_w, p[:, g0:g0 + H * vdim], self.eps, og)
+        gate = p[:, g0:g0 + H * vdim]
+        if self.norm == "all_heads" and self.gate == "sigmoid":
+            K.norm_gate_rows(o, self.norm_w, gate, self.eps, og)
+        else:
+            K.group_norm_gate_rows(o, self.norm_w, gate, self.eps, og, H if self.norm == "per_head" else 1, False, self.gate)
         linear(og, self.w_o, out=residual, accumulate=True)
 
 

@@ -1,8 +1,12 @@
-"""RMSNorm over the rows of the residual.
+"""Norms over the rows of the residual: RMSNorm, and a weighted layer norm without a shift.
 
 ``y = (x * rsqrt(mean(x^2) + eps)) * w`` with float32 statistics
 (src/backend/cpu/scalar/quants.c:1489-1512).  The input is the float32
 residual; the output has the compute dtype (it feeds a matrix product).
+
+``layernorm``: ``y = (x - mean(x)) * rsqrt(var(x) + eps) * w`` with the variance
+taken about the mean (the mean of the squared deviations), float32 statistics,
+no bias.
 """
 from __future__ import annotations
 
@@ -36,4 +40,14 @@ class RMSNorm(Part):
         return K.rmsnorm_rows(x, self.weight, self.eps, out, rows)
 
 
+class LayerNorm(RMSNorm):
+    """Same sizes, weight and interface as :class:`RMSNorm`; the rows are centred first."""
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=self.env.dtype, device=x.device)
+        return K.layernorm_rows(x, self.weight, self.eps, out, rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
