@@ -42,6 +42,11 @@ attention with decay, tanh-gelu gated units and mixtures with identity and share
 layers, learned positions, per-layer token inputs) beside a Tizusun model of the same layer sizes, the closest
 design the engine has (gated attention, dense and mixture feed-forwards, whole softmax weights).
 
+``--design tupalorn`` does the same for the Tupalorn design (parallel layers behind one layer norm: a state space
+mixer, retention, windowed attention with norms over whole projections and head gates, one of them reading another
+layer's keys and values; clamped gated units with biases; a soft cap on the logits) beside a Vekuzen model of dense
+layers of the same sizes (latent attention and lightning layers in turn), the closest design the engine has.
+
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and
 exits with 2.
 """
@@ -436,6 +441,24 @@ def vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers):
     return cfg
 
 
+TUPALORN_WINDOW = 1024
+
+
+def tupalorn_config(width, H, G, hd, ff):
+    """Four layers of the sizes of the other designs': a state space mixer (twice the width inside, heads of 64, a
+    state of 128 rows, one group, four taps), retention with the attention's heads, attention over the whole context
+    and an attention layer that reads its keys and values through a shorter window."""
+    ssm = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    ret = {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-3 - 6 * h / max(1, H - 1)) for h in range(H)],
+           "rot": {"dims": hd, "base": 1000000.0}}
+    att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_BLOCK}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    mixers = [("mamba2", ssm), ("retention", ret), ("attention", att),
+              ("attention", dict(att, kv_from=2, mask={"size": TUPALORN_WINDOW}))]
+    return {"architecture": "Tupalorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(mlp)} for t, m in mixers]}
+
+
 def lfm2_like_config(width, H, G, hd, ff, n_layers):
     return dict(architectures=["Lfm2ForCausalLM"], vocab_size=DESIGN_VOCAB, hidden_size=width, num_hidden_layers=n_layers,
                 num_attention_heads=H, num_key_value_heads=G, head_dim=hd, layer_types=["full_attention"] * n_layers,
@@ -487,8 +510,10 @@ def run_design(a) -> int:
     warmup = max(a.warmup, 3)
     steps = min(a.steps, 128)
     vekuzen = a.design == "vekuzen"
-    out = {"design": "Vekuzen" if vekuzen else "Tizusun",
-           "beside": "Tizusun layers of the same sizes" if vekuzen else "LFM2 attention layers of the same sizes", "dtype": "bf16",
+    tupalorn = a.design == "tupalorn"
+    out = {"design": a.design.capitalize(),
+           "beside": ("dense Vekuzen layers of the same sizes" if tupalorn else "Tizusun layers of the same sizes" if vekuzen
+                      else "LFM2 attention layers of the same sizes"), "dtype": "bf16",
            "softmax_weights": a.softmax_weights,
            "data": "synthetic: random weights, uniform random token ids", "prompt_tokens": T, "decode_batch": B,
            "decode_context": f"{T} to {ctx_len}", "peaks": pk, "sizes": {}}
@@ -498,7 +523,11 @@ def run_design(a) -> int:
         if a.size and a.size != name:
             continue
         rec = {}
-        pair = ((("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers)),
+        if tupalorn:
+            layers = "dddd"
+        pair = ((("tupalorn", tupalorn_config(width, H, G, hd, ff)),
+                 ("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers))) if tupalorn else
+                (("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers)),
                  ("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers))) if vekuzen else
                 (("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers)),
                  ("lfm2", lfm2_like_config(width, H, G, hd, ff, len(layers)))))
@@ -645,9 +674,9 @@ def main() -> int:
                     help="with --workload: launch every kernel on its own between CUDA events and print the device "
                          "time by kernel class (the run's throughput is then not the engine's)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
-    ap.add_argument("--design", choices=["tizusun", "vekuzen"], default=None,
+    ap.add_argument("--design", choices=["tizusun", "vekuzen", "tupalorn"], default=None,
                     help="time another design at a few layer sizes beside the closest existing model of the same sizes "
-                         "(tizusun beside LFM2 attention layers, vekuzen beside tizusun) "
+                         "(tizusun beside LFM2 attention layers, vekuzen beside tizusun, tupalorn beside dense vekuzen layers) "
                          "(prefill, decode, device time by kernel class) instead of the default line")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only (e.g. 2048x32h64)")
     ap.add_argument("--softmax-weights", choices=["float32", "operand"], default="float32",

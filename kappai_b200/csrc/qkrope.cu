@@ -243,7 +243,7 @@ extern "C" int kp_qk_rownorm_kv(const void* qkv, int ld, int k_col, int v_col, c
                                 int page_size, int n, int H, int G, int hd, int write_kv, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (H < 1 || G < 1 || hd < 1 || !q_w || !q_out || (write_kv && (!k_w || !cache || !slot_map))) return KP_ERR_BAD_ARG;
-    if (!(count_q > 0.f) || !(count_k > 0.f)) return KP_ERR_BAD_ARG;
+    if (!(count_q > 0.f) || (write_kv && !(count_k > 0.f))) return KP_ERR_BAD_ARG;
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(qk_rownorm_kv_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)qkv, ld,
                                                k_col, v_col, q_w, k_w, eps, count_q, count_k, slot_map, (T*)q_out, ldq, (T*)cache,
                                                page_size, H, G, hd, write_kv)));
