@@ -35,6 +35,7 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __f
 #define KP_ACT_SILU 0
 #define KP_ACT_RELU 1
 #define KP_ACT_GELU_TANH 2
+#define KP_ACT_GLU_CLAMPED 3      // the gated unit with limits below; only the products' gated epilogues take this code
 template <int ACT> __device__ __forceinline__ float kp_act(float g) {
     if (ACT == KP_ACT_RELU) return fmaxf(g, 0.f);
     if (ACT == KP_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
@@ -57,6 +58,11 @@ __device__ __forceinline__ float kp_glu_clamped(float g, float u, float limit, f
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return (g / (1.0f + expf(-alpha * g))) * (u + shift);
+}
+// What a product's gated epilogue makes of a gate and an up value (both already rounded to the storage type).
+__device__ __forceinline__ float kp_gated_epilogue(int act, float g, float u, float limit, float alpha, float shift) {
+    if (act == KP_ACT_GLU_CLAMPED) return kp_glu_clamped(g, u, limit, alpha, shift);
+    return kp_act_epilogue(act, g) * u;
 }
 #define KP_EPI_ACT(epi) (((epi) >> 8) & 0xff)
 #define KP_EPI_KIND(epi) ((epi) & 0xff)

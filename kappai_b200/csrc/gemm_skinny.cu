@@ -56,6 +56,7 @@ struct SkinnyArgs {
     void* C; int ldc;
     int M, N, K, ff;
     int act;                             // activation of the gated epilogue (common.cuh)
+    float glu_limit, glu_alpha, glu_shift;  // constants of the gated unit with limits (act == KP_ACT_GLU_CLAMPED)
 };
 
 // MT: m16 tiles of batch rows; HALF: only rows 0..7 of the single tile exist (M <= 8).
@@ -162,7 +163,7 @@ gemm_skinny_kernel(const SkinnyArgs p) {
             if (p.bias) u += p.bias[p.ff + n];
             // gate and up are rounded to the storage type before the activation, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-            ((bf16*)p.C)[o] = from_f32<bf16>(kp_act_epilogue(p.act, gq) * uq);
+            ((bf16*)p.C)[o] = from_f32<bf16>(kp_gated_epilogue(p.act, gq, uq, p.glu_limit, p.glu_alpha, p.glu_shift));
         } else if (EPI == EPI_STORE) {
             ((bf16*)p.C)[o] = from_f32<bf16>(v);
         } else if (EPI == EPI_STORE_F32) {
@@ -223,13 +224,29 @@ static int check_common(int M, int N, int K, int ldw, const void* W, int epi, in
 extern "C" {
 
 // epi: 0 store bf16, 1 store f32, 2 accumulate f32, 3 SwiGLU (N = 2*ff rows of W, output [M, ff] bf16)
+static int skinny_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                      int K, int epi, const float* glu, void* stream);
+
 int kp_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                    int K, int epi, void* stream) {
+    return skinny_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, nullptr, stream);
+}
+
+// the same with the constants of the gated unit with limits (activation code 3 in epi)
+int kp_gemm_skinny_glu(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                       int K, int epi, float limit, float alpha, float shift, void* stream) {
+    const float glu[3] = {limit, alpha, shift};
+    return skinny_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, glu, stream);
+}
+
+static int skinny_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                      int K, int epi, const float* glu, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     SkinnyArgs a = {};
     a.act = KP_EPI_ACT(epi);
     epi = KP_EPI_KIND(epi);
-    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU && a.act != KP_ACT_GELU_TANH) return KP_ERR_UNSUPPORTED;
+    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU && a.act != KP_ACT_GELU_TANH && !(a.act == KP_ACT_GLU_CLAMPED && glu)) return KP_ERR_UNSUPPORTED;
+    if (glu) { a.glu_limit = glu[0]; a.glu_alpha = glu[1]; a.glu_shift = glu[2]; }
     int st = check_common(M, N, K, ldw, W, epi, &a.ff);
     if (st) return st;
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;

@@ -87,6 +87,7 @@ struct StreamArgs {
     int M, N, K, ff;                     // ff: output columns of an epilogue that joins rows of W (SwiGLU: N / 2; conv step: N / 3)
     int n_stages;                        // stages of the ring
     int act;                             // activation of the gated epilogue (common.cuh)
+    float glu_limit, glu_alpha, glu_shift;  // constants of the gated unit with limits (act == KP_ACT_GLU_CLAMPED)
     // the conv step (EPI_CONV_STEP): taps [ff][conv_k], optional bias [ff], state [slots][conv_k - 1][ff], and for
     // every row its position (0: the state counts as zero) and its state slot
     const float* conv_w; const float* conv_bias; float* conv_state;
@@ -318,7 +319,7 @@ gemm_stream_kernel(const StreamArgs p) {
                 if (p.bias) u += p.bias[p.ff + n];
                 // gate and up are rounded to the storage type before the activation, as the unfused path stores them
                 const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-                ((bf16*)p.C)[o] = from_f32<bf16>(kp_act_epilogue(p.act, gq) * uq);
+                ((bf16*)p.C)[o] = from_f32<bf16>(kp_gated_epilogue(p.act, gq, uq, p.glu_limit, p.glu_alpha, p.glu_shift));
             } else if (EPI == EPI_STORE) {
                 ((bf16*)p.C)[o] = from_f32<bf16>(v);
             } else if (EPI == EPI_STORE_F32) {
@@ -419,13 +420,29 @@ static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void*
 
 extern "C" {
 
+// glu: limit, alpha and shift of the gated unit with limits (activation code 3 in epi), else null.
+static int stream_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                      int K, int epi, const float* glu, void* stream);
+
 int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                    int K, int epi, void* stream) {
+    return stream_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, nullptr, stream);
+}
+
+int kp_gemm_stream_glu(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                       int K, int epi, float limit, float alpha, float shift, void* stream) {
+    const float glu[3] = {limit, alpha, shift};
+    return stream_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, glu, stream);
+}
+
+static int stream_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                      int K, int epi, const float* glu, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     StreamArgs a = {};
     a.act = KP_EPI_ACT(epi);
     epi = KP_EPI_KIND(epi);
-    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU && a.act != KP_ACT_GELU_TANH) return KP_ERR_UNSUPPORTED;
+    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU && a.act != KP_ACT_GELU_TANH && !(a.act == KP_ACT_GLU_CLAMPED && glu)) return KP_ERR_UNSUPPORTED;
+    if (glu) { a.glu_limit = glu[0]; a.glu_alpha = glu[1]; a.glu_shift = glu[2]; }
     int st = check_common(a, M, N, K, ldw, W, epi);
     if (st) return st;
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;

@@ -55,6 +55,7 @@ struct TcArgs {
     void* C; int ldc;
     int M, N, K, ff;
     int act;                                // activation of the gated epilogue (common.cuh)
+    float glu_limit, glu_alpha, glu_shift;  // constants of the gated unit with limits (act == KP_ACT_GLU_CLAMPED)
     int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
     int a_rows;                             // rows of the A box: 128, fewer (a multiple of 8) when M < 128
     int n_stages;                           // stages of the ring
@@ -99,7 +100,7 @@ __device__ __forceinline__ void tc_finish(const TcArgs& p, int n_lim, const floa
             if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
             // gate and up are rounded to the storage type first, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-            x = kp_act_epilogue(p.act, gq) * uq;
+            x = kp_gated_epilogue(p.act, gq, uq, p.glu_limit, p.glu_alpha, p.glu_shift);
         }
         v[j] = x;
     }
@@ -521,16 +522,32 @@ extern "C" {
 
 // epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16).
 // split: products of 17 to 1024 rows may be cut along K (0: never).
+// glu: limit, alpha and shift of the gated unit with limits (activation code 3 in epi), else null.
+static int tc_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                  int K, int epi, int split, const float* glu, void* stream);
+
 int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                      int K, int epi, int split, void* stream) {
+    return tc_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, split, nullptr, stream);
+}
+
+int kp_gemm_tc_split_glu(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                         int K, int epi, int split, float limit, float alpha, float shift, void* stream) {
+    const float glu[3] = {limit, alpha, shift};
+    return tc_run(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, split, glu, stream);
+}
+
+static int tc_run(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                  int K, int epi, int split, const float* glu, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     const int act = KP_EPI_ACT(epi);
     epi = KP_EPI_KIND(epi);
-    if (act != KP_ACT_SILU && act != KP_ACT_RELU && act != KP_ACT_GELU_TANH) return KP_ERR_UNSUPPORTED;
+    if (act != KP_ACT_SILU && act != KP_ACT_RELU && act != KP_ACT_GELU_TANH && !(act == KP_ACT_GLU_CLAMPED && glu)) return KP_ERR_UNSUPPORTED;
     if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
     TcArgs a = {};
     a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.ff = 0; a.act = act;
+    if (glu) { a.glu_limit = glu[0]; a.glu_alpha = glu[1]; a.glu_shift = glu[2]; }
     {
         const int esz = (epi == EPI_STORE || epi == EPI_SWIGLU) ? 2 : 4;
         a.vec_ok = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * esz) % 16 == 0) ? 1 : 0;

@@ -167,26 +167,45 @@ __device__ __forceinline__ void lc_stage_transposed(float* dst, const T* __restr
                                                     int t0, int n, int tid, const LcRot rp) {
     const int half = rp.rot >> 1;
     if (VEC && (half % 8 == 0)) {
-        const int ng = dim / 8;
-        for (int x = tid; x < ng * LC_C; x += LC_THREADS) {
-            const int t = x % LC_C, g = x / LC_C;
-            uint4 raw = make_uint4(0u, 0u, 0u, 0u), praw = raw;
-            const bool rotated = g * 8 < rp.rot, lowr = g * 8 < half;
+        // an item is (row t, eight columns): a rotated pair of eights (columns g 8 .. and half + g 8 ..) is one item, so
+        // that both halves and their cosines and sines are fetched once, 16 bytes a load
+        const int ng = dim / 8, hg = half / 8;
+        for (int x = tid; x < (ng - hg) * LC_C; x += LC_THREADS) {
+            const int t = x % LC_C, j = x / LC_C;
+            const bool pair = j < hg;
+            const int g = pair ? j : j + hg;
+            float lo8[8], hi8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) lo8[e] = hi8[e] = 0.f;
             if (t < n) {
                 const T* src = qkv + (size_t)(t0 + t) * ld + col + head * dim + g * 8;
-                raw = __ldg(reinterpret_cast<const uint4*>(src));
-                if (rotated) praw = __ldg(reinterpret_cast<const uint4*>(lowr ? src + half : src - half));
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+                const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 8; e++) lo8[e] = lt_act<ACT>(__bfloat162float(e8[e]));
+                if (pair) {
+                    const uint4 praw = __ldg(reinterpret_cast<const uint4*>(src + half));
+                    const bf16* p8 = reinterpret_cast<const bf16*>(&praw);
+                    const float4* ct = reinterpret_cast<const float4*>(rp.cos_tab + (size_t)(rp.pos0 + t) * half + g * 8);
+                    const float4* st = reinterpret_cast<const float4*>(rp.sin_tab + (size_t)(rp.pos0 + t) * half + g * 8);
+                    const float4 c0 = __ldg(ct), c1 = __ldg(ct + 1), s0 = __ldg(st), s1 = __ldg(st + 1);
+                    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const float u = lo8[e], w = lt_act<ACT>(__bfloat162float(p8[e]));
+                        float a = u, b = w;
+                        lt_rotate(a, w, cs[e], sn[e], true);
+                        lt_rotate(b, u, cs[e], sn[e], false);
+                        lo8[e] = a;
+                        hi8[e] = b;
+                    }
+                }
             }
-            const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
-            const bf16* p8 = reinterpret_cast<const bf16*>(&praw);
 #pragma unroll
             for (int e = 0; e < 8; e++) {
-                float v = t < n ? lt_act<ACT>(__bfloat162float(e8[e])) : 0.f;
-                if (rotated && t < n) {
-                    const size_t tb = (size_t)(rp.pos0 + t) * half + (lowr ? g * 8 + e : g * 8 + e - half);
-                    lt_rotate(v, lt_act<ACT>(__bfloat162float(p8[e])), rp.cos_tab[tb], rp.sin_tab[tb], lowr);
-                }
-                dst[(g * 8 + e) * LC_LD + t] = v * rp.scale;
+                dst[(g * 8 + e) * LC_LD + t] = lo8[e] * rp.scale;
+                if (pair) dst[(half + g * 8 + e) * LC_LD + t] = hi8[e] * rp.scale;
             }
         }
     } else {

@@ -426,6 +426,51 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(((src[i] - mean) * scale) * w[i]);
 }
 
+// The same for rows of at most 8192 floats (a multiple of 4) that are 16-byte aligned: each thread keeps its 8 float4
+// of the row in registers, so the row is read once; mean first, then the squared deviations about it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+layernorm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                          const int* __restrict__ rows, int d, float eps) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+    const int n4 = d >> 2;
+    float4 v[8];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < n4 ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = block_sum(s, red) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean;
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    T* dst = y + (size_t)r * d;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 ww = __ldg(w4 + i);
+            store4(dst + 4 * i, (v[j].x * scale) * ww.x, (v[j].y * scale) * ww.y, (v[j].z * scale) * ww.z,
+                   (v[j].w * scale) * ww.w);
+        }
+    }
+}
+
 // RMS norm of float32 rows cut into `groups` stretches of equal width, every stretch with a mean square of its own,
 // and a gate from rows in the storage type: gate_first ? norm(o * act(g)) * w : norm(o) * w * act(g); w may be null (no weight); act is silu
 // (gate_act 0) or the sigmoid (1).  A block takes one (row, part); its size depends on the part's width alone.
@@ -461,6 +506,69 @@ group_norm_gate_rows_kernel(const float* __restrict__ o, int ldo, const float* _
     }
 }
 
+__device__ __forceinline__ float4 load4(const float* src) { return *reinterpret_cast<const float4*>(src); }
+__device__ __forceinline__ float4 load4(const bf16* src) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float gn_gate(float z, int gate_act) {
+    const float sg = 1.0f / (1.0f + expf(-z));
+    return gate_act == 0 ? z * sg : sg;
+}
+
+// The same where a part is a multiple of 4 wide, at most 16 TEAM columns, and rows and parts start on 16 bytes (8 in
+// bfloat16): TEAM threads (a warp, or the block) take one (row, part) and keep it and its gates in registers, so both
+// are read once and every gate's exponential is taken once.  Which form runs depends on the part's width alone.
+template <typename T, int TEAM>
+__global__ void __launch_bounds__(256)
+group_norm_gate_rows_vec_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, const T* __restrict__ g, int ldg,
+                                T* __restrict__ out, int ldout, int n_items, int groups, int width, float eps, int gate_first,
+                                int gate_act) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int team = threadIdx.x / TEAM, lane = threadIdx.x % TEAM;
+    const int item = blockIdx.x * (256 / TEAM) + team;
+    const bool live = item < n_items;                      // (a whole team at once; with TEAM == 256 always true)
+    const int r = live ? item / groups : 0, c0 = live ? (item % groups) * width : 0;
+    const float* src = o + (size_t)r * ldo + c0;
+    const T* gr = g + (size_t)r * ldg + c0;
+    const int n4 = width >> 2;
+    float4 v[4], gt[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int i = lane + j * TEAM;
+        v[j] = gt[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && i < n4) {
+            v[j] = load4(src + 4 * i);
+            const float4 z = load4(gr + 4 * i);
+            gt[j] = make_float4(gn_gate(z.x, gate_act), gn_gate(z.y, gate_act), gn_gate(z.z, gate_act), gn_gate(z.w, gate_act));
+            if (gate_first) { v[j].x *= gt[j].x; v[j].y *= gt[j].y; v[j].z *= gt[j].z; v[j].w *= gt[j].w; }
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    ss = TEAM == 32 ? warp_sum(ss) : block_sum(ss, red);
+    if (!live) return;
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    T* dst = out + (size_t)r * ldout + c0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int i = lane + j * TEAM;
+        if (i < n4) {
+            float4 y = make_float4(v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale);
+            if (w) {
+                const float4 ww = load4(w + c0 + 4 * i);
+                y.x *= ww.x; y.y *= ww.y; y.z *= ww.z; y.w *= ww.w;
+            }
+            if (!gate_first) { y.x *= gt[j].x; y.y *= gt[j].y; y.z *= gt[j].z; y.w *= gt[j].w; }
+            store4(dst + 4 * i, y.x, y.y, y.z, y.w);
+        }
+    }
+}
+
 // o[r, h * hd + i] *= sigmoid(g[r, h]): one gate a head.
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ o, int ldo, const T* __restrict__ g, int ldg, int n, int H, int hd) {
@@ -471,6 +579,21 @@ __global__ void head_gate_kernel(T* __restrict__ o, int ldo, const T* __restrict
         const float z = to_f32(g[r * ldg + c / hd]);
         T* p = o + r * ldo + c;
         *p = from_f32<T>(to_f32(*p) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+// The same, four columns a thread (head sizes that are multiples of 4, rows that start on 16 bytes, 8 in bfloat16).
+template <typename T>
+__global__ void head_gate_vec_kernel(T* __restrict__ o, int ldo, const T* __restrict__ g, int ldg, int n, int H, int hd) {
+    kp_pdl_begin();
+    const size_t cols4 = (size_t)H * hd / 4, total = (size_t)n * cols4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols4, c = (i % cols4) * 4;
+        const float z = to_f32(g[r * ldg + c / hd]);
+        const float sg = 1.0f / (1.0f + expf(-z));
+        T* p = o + r * ldo + c;
+        const float4 v = load4(p);
+        store4(p, v.x * sg, v.y * sg, v.z * sg, v.w * sg);
     }
 }
 
@@ -697,7 +820,13 @@ int kp_gather_status(const unsigned long long* addrs, int n, int* out, void* str
 int kp_layernorm_rows(const float* x, const float* w, void* y, const int* rows, int n, int d, float eps, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (d < 1) return KP_ERR_BAD_ARG;
-    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(layernorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
+    // rows of at most 8192 floats that start on 16 bytes: the row is read once and stays in registers
+    const bool vec = (d % 4 == 0) && d <= 8192 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0);
+    if (vec) {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(layernorm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
+    } else {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(layernorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
+    }
     return kp_launch_status();
 }
 
@@ -707,6 +836,24 @@ int kp_group_norm_gate_rows(const float* o, int ldo, const float* w, const void*
     if (n <= 0) return 0;
     if (groups < 1 || width < 1 || gate_act < 0 || gate_act > 1) return KP_ERR_BAD_ARG;
     if (groups > 65535) return KP_ERR_UNSUPPORTED;
+    {
+        const int esz = dtype == KP_DTYPE_F32 ? 4 : 2;
+        const bool aligned = width % 4 == 0 && ldo % 4 == 0 && ldg % 4 == 0 && ldout % 4 == 0 && (uintptr_t)o % 16 == 0 &&
+                             (!w || (uintptr_t)w % 16 == 0) && (uintptr_t)g % (4 * esz) == 0 && (uintptr_t)out % (4 * esz) == 0;
+        const long long items = (long long)n * groups;
+        if (aligned && width <= 4096 && items < (1ll << 31)) {
+            if (width <= 512) {
+                KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(group_norm_gate_rows_vec_kernel<T, 32>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0,
+                                                           (cudaStream_t)stream, o, ldo, w, (const T*)g, ldg, (T*)out, ldout, (int)items,
+                                                           groups, width, eps, gate_first, gate_act)));
+            } else {
+                KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(group_norm_gate_rows_vec_kernel<T, 256>, dim3((unsigned)items), dim3(256), 0,
+                                                           (cudaStream_t)stream, o, ldo, w, (const T*)g, ldg, (T*)out, ldout, (int)items,
+                                                           groups, width, eps, gate_first, gate_act)));
+            }
+            return kp_launch_status();
+        }
+    }
     const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;      // by the part's width alone
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(group_norm_gate_rows_kernel<T>, dim3(n, groups), dim3(threads), 0, (cudaStream_t)stream, o,
                                                ldo, w, (const T*)g, ldg, (T*)out, ldout, width, eps, gate_first, gate_act)));
@@ -716,6 +863,13 @@ int kp_group_norm_gate_rows(const float* o, int ldo, const float* w, const void*
 int kp_head_gate(void* o, int ldo, const void* g, int ldg, int n, int H, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (H < 1 || hd < 1) return KP_ERR_BAD_ARG;
+    const int esz = dtype == KP_DTYPE_F32 ? 4 : 2;
+    if (hd % 4 == 0 && ldo % 4 == 0 && (uintptr_t)o % (4 * esz) == 0) {
+        const int gv = grid_for((size_t)n * H * hd / 4, 256);
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(head_gate_vec_kernel<T>, dim3(gv), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo,
+                                                   (const T*)g, ldg, n, H, hd)));
+        return kp_launch_status();
+    }
     const int gr = grid_for((size_t)n * H * hd, 256);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(head_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo, (const T*)g,
                                                ldg, n, H, hd)));

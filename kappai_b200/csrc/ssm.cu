@@ -68,6 +68,125 @@ ssm_conv_kernel(const T* __restrict__ p, int ld, int conv_col, int dt_col, const
     }
 }
 
+// The same for prompt portions where rows and channels start on 16 bytes and K <= 4: a thread takes 16 bytes of
+// channels (VW of them) of SV_ROWS consecutive rows and fetches every row of p once for all of them.  Every output is
+// the same chain of multiply-adds as above (bias, then the taps from the oldest), so a row's bits do not depend on
+// which form ran.  The last blocks along x compute dt and the decay's logarithm of the tile's rows.
+#define SV_ROWS 4
+template <typename T> struct SsVec;
+template <> struct SsVec<bf16> {
+    static constexpr int W = 8;
+    __device__ static void load(const bf16* src, float* v) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+        const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __bfloat162float(e[i]);
+    }
+    __device__ static void store(bf16* dst, const float* v) {
+        uint4 o;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+        *reinterpret_cast<uint4*>(dst) = o;
+    }
+};
+template <> struct SsVec<float> {
+    static constexpr int W = 4;
+    __device__ static void load(const float* src, float* v) {
+        const float4 r = __ldg(reinterpret_cast<const float4*>(src));
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    __device__ static void store(float* dst, const float* v) { *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+
+template <typename T, int K>
+__global__ void __launch_bounds__(128)
+ssm_conv_vec_kernel(const T* __restrict__ p, int ld, int conv_col, int dt_col, const float* __restrict__ taps,
+                    const float* __restrict__ bias, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                    const float* __restrict__ kept, size_t slot_stride, const int* __restrict__ row_seg,
+                    const int* __restrict__ cu_rows, const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
+                    T* __restrict__ out, float* __restrict__ dt_out, float* __restrict__ da_out, int n, int C, int H, int conv_blocks) {
+    kp_pdl_begin();
+    constexpr int W = SsVec<T>::W;
+    const int r0 = blockIdx.y * SV_ROWS;
+    if ((int)blockIdx.x >= conv_blocks) {
+        for (int x = (blockIdx.x - conv_blocks) * blockDim.x + threadIdx.x; x < SV_ROWS * H; x += (gridDim.x - conv_blocks) * blockDim.x) {
+            const int r = r0 + x / H, h = x % H;
+            if (r < n) {
+                const float dt = ss_softplus(to_f32(p[(size_t)r * ld + dt_col + h]) + dt_bias[h]);
+                dt_out[(size_t)r * H + h] = dt;
+                da_out[(size_t)r * H + h] = -expf(a_log[h]) * dt;
+            }
+        }
+        return;
+    }
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * W;
+    if (c >= C) return;
+    // rows r0 - (K - 1) .. r0 + SV_ROWS - 1 of this step (zero where there is none; whether a row counts is decided below)
+    float win[SV_ROWS + K - 1][W];
+#pragma unroll
+    for (int i = 0; i < SV_ROWS + K - 1; i++) {
+        const int rr = r0 - (K - 1) + i;
+        if (rr >= 0 && rr < n) SsVec<T>::load(p + (size_t)rr * ld + conv_col + c, win[i]);
+        else {
+#pragma unroll
+            for (int e = 0; e < W; e++) win[i][e] = 0.f;
+        }
+    }
+    // the thread's W K taps lie side by side and start on 32 bytes (c is a multiple of W): 16 bytes a load
+    float tp[W][K], bs[W];
+    {
+        float flat[W * K];
+        const float4* t4 = reinterpret_cast<const float4*>(taps + (size_t)c * K);
+#pragma unroll
+        for (int i = 0; i < W * K / 4; i++) {
+            const float4 t = __ldg(t4 + i);
+            flat[4 * i] = t.x; flat[4 * i + 1] = t.y; flat[4 * i + 2] = t.z; flat[4 * i + 3] = t.w;
+        }
+        const float4* b4 = reinterpret_cast<const float4*>(bias + c);
+#pragma unroll
+        for (int i = 0; i < W / 4; i++) {
+            const float4 t = __ldg(b4 + i);
+            bs[4 * i] = t.x; bs[4 * i + 1] = t.y; bs[4 * i + 2] = t.z; bs[4 * i + 3] = t.w;
+        }
+#pragma unroll
+        for (int e = 0; e < W; e++)
+#pragma unroll
+            for (int j = 0; j < K; j++) tp[e][j] = flat[e * K + j];
+    }
+#pragma unroll
+    for (int i = 0; i < SV_ROWS; i++) {
+        const int r = r0 + i;
+        if (r >= n) break;
+        const int seg = row_seg[r], row0 = cu_rows[seg];
+        const bool fresh = seg_pos[seg] == 0;
+        const float* kp = kept + (size_t)seg_slot[seg] * slot_stride;
+        float acc[W];
+#pragma unroll
+        for (int e = 0; e < W; e++) acc[e] = bs[e];
+#pragma unroll
+        for (int j = 0; j < K; j++) {
+            const int rr = r - (K - 1) + j;
+            if (rr >= row0) {
+#pragma unroll
+                for (int e = 0; e < W; e++) acc[e] = fmaf(tp[e][j], win[i + j][e], acc[e]);
+            } else if (!fresh) {
+                const float* kr = kp + (size_t)(rr - row0 + K - 1) * C + c;
+#pragma unroll
+                for (int e = 0; e < W; e++) acc[e] = fmaf(tp[e][j], kr[e], acc[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < W; e++) acc[e] = fmaf(tp[e][j], 0.f, acc[e]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < W; e++) acc[e] = ss_silu(acc[e]);
+        SsVec<T>::store(out + (size_t)r * C + c, acc);
+    }
+}
+
 // The inputs a request keeps behind a segment of len rows: its last taps - 1, from the rows of this step and, where the
 // segment is shorter than that, from what was kept before (zero for a fresh sequence).
 template <typename T>
@@ -422,9 +541,23 @@ int kp_ssm_conv(const void* p, int ld, int conv_col, int dt_col, const float* ta
     if (C < 1 || H < 1 || K < 1 || K > SS_MAX_TAPS || n > 65535 || n_seg > 65535) return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int fused = single_rows && keep;
-    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(ssm_conv_kernel<T>, dim3((C + H + 127) / 128, n), dim3(128), 0, s, (const T*)p, ld, conv_col,
-                                               dt_col, taps, bias, dt_bias, a_log, kept, (size_t)slot_stride, row_seg, cu_rows, seg_pos,
-                                               seg_slot, (T*)out, dt_out, da_out, C, H, K, fused)));
+    const int vw = dtype == KP_DTYPE_F32 ? 4 : 8;
+    const bool vec = !single_rows && K <= 4 && n >= 2 * SV_ROWS && C % vw == 0 && ld % vw == 0 && conv_col % vw == 0 &&
+                     (uintptr_t)p % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)taps % 16 == 0 && (uintptr_t)bias % 16 == 0;
+    if (vec) {
+        const int conv_blocks = (C / vw + 127) / 128, dt_blocks = (SV_ROWS * H + 127) / 128 > 4 ? 4 : (SV_ROWS * H + 127) / 128;
+        const dim3 grid(conv_blocks + dt_blocks, (n + SV_ROWS - 1) / SV_ROWS);
+#define SV_LAUNCH(KK)                                                                                                        \
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(ssm_conv_vec_kernel<T, KK>, grid, dim3(128), 0, s, (const T*)p, ld, conv_col, dt_col, taps,  \
+                                                   bias, dt_bias, a_log, (const float*)kept, (size_t)slot_stride, row_seg, cu_rows, seg_pos, \
+                                                   seg_slot, (T*)out, dt_out, da_out, n, C, H, conv_blocks)))
+        if (K == 1) SV_LAUNCH(1); else if (K == 2) SV_LAUNCH(2); else if (K == 3) SV_LAUNCH(3); else SV_LAUNCH(4);
+#undef SV_LAUNCH
+    } else {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(ssm_conv_kernel<T>, dim3((C + H + 127) / 128, n), dim3(128), 0, s, (const T*)p, ld, conv_col,
+                                                   dt_col, taps, bias, dt_bias, a_log, kept, (size_t)slot_stride, row_seg, cu_rows, seg_pos,
+                                                   seg_slot, (T*)out, dt_out, da_out, C, H, K, fused)));
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (keep && !fused && K > 1) {

@@ -7,7 +7,7 @@ that is not on a CUDA device is refused.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -1038,9 +1038,11 @@ def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, swiglu: bool = False, split: bool = True, activation: str = "silu") -> torch.Tensor:
+            accumulate: bool = False, swiglu: bool = False, split: bool = True, activation: str = "silu",
+            glu: Optional[Tuple[float, float, float]] = None) -> torch.Tensor:
     """out = a @ w.T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); with
-    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up.  With ``split`` a product of 17 to
+    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up (or ``activation``; with ``glu`` =
+    (limit, alpha, shift) the gated unit with limits of :func:`glu_clamped`).  With ``split`` a product of 17 to
     1024 rows is cut along K where that brings fewer bytes into the busiest SM (the parts of a tile are a
     thread-block cluster and are added in a fixed order)."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
@@ -1054,8 +1056,14 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         _need(bias, "bias", torch.float32)
         if bias.numel() != N:
             raise KernelError("gemm_tc: bias size")
-    epi = _skinny_epilogue(out, accumulate, swiglu) | (_fused_activation(activation) << 8 if swiglu else 0)
     lib = load_library("gemm_tc")
+    if swiglu and glu is not None:
+        epi = _skinny_epilogue(out, accumulate, swiglu) | (ACT_GLU_CLAMPED << 8)
+        _run("gemm_tc", lib.kp_gemm_tc_split_glu, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+             _rows_2d(out, "out"), M, N, K, epi, 1 if split else 0, *_glu_floats(glu), STREAM, tag=f" {N}x{K}",
+             work=_gemm_work(M, N, K, a, w, out))
+        return out
+    epi = _skinny_epilogue(out, accumulate, swiglu) | (_fused_activation(activation) << 8 if swiglu else 0)
     _run("gemm_tc", lib.kp_gemm_tc_split, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
          _rows_2d(out, "out"), M, N, K, epi, 1 if split else 0, STREAM, tag=f" {N}x{K}",
          work=_gemm_work(M, N, K, a, w, out))
@@ -1119,6 +1127,14 @@ def gemm_stream_conv_step(a: torch.Tensor, w_in: torch.Tensor, bias: Optional[to
 
 
 FUSED_ACTIVATIONS = ("silu", "relu", "gelu_tanh")     # what the products' gated epilogues compute themselves
+ACT_GLU_CLAMPED = 3        # the epilogues' code of the gated unit with limits (csrc/common.cuh); its constants travel beside it
+
+
+def _glu_floats(glu):
+    limit, alpha, shift = glu
+    if not limit > 0:
+        raise KernelError("the gated unit's limit must be positive")
+    return ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift)
 
 
 def _fused_activation(name: str) -> int:
@@ -1144,9 +1160,11 @@ def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                accumulate: bool = False, swiglu: bool = False, activation: str = "silu") -> torch.Tensor:
+                accumulate: bool = False, swiglu: bool = False, activation: str = "silu",
+                glu: Optional[Tuple[float, float, float]] = None) -> torch.Tensor:
     """out = a @ w.T (+ bias) for up to 64 rows of bfloat16 ``a``.  With
-    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up."""
+    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up (or ``activation``; with ``glu`` =
+    (limit, alpha, shift) the gated unit with limits of :func:`glu_clamped`)."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
     _need(out, "out", contiguous=False)
     M, K = a.shape
@@ -1161,7 +1179,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     if swiglu:
         if out.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: the SwiGLU epilogue writes bfloat16")
-        epi = EPI_SWIGLU | (_fused_activation(activation) << 8)
+        epi = EPI_SWIGLU | ((ACT_GLU_CLAMPED if glu is not None else _fused_activation(activation)) << 8)
     elif accumulate:
         if out.dtype != torch.float32:
             raise KernelError("gemm_skinny: accumulation needs a float32 output")
@@ -1172,14 +1190,17 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
         epi = EPI_STORE_F32
     else:
         raise KernelError("gemm_skinny: output dtype")
+    consts = _glu_floats(glu) if swiglu and glu is not None else ()
     if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K) and M <= STREAM_MAX_M:
         lib = load_library("gemm_stream")
-        _run("gemm_stream", lib.kp_gemm_stream, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-             _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
+        _run("gemm_stream", lib.kp_gemm_stream_glu if consts else lib.kp_gemm_stream, _ptr(a), _rows_2d(a, "a"), _ptr(w),
+             _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, epi, *consts, STREAM, tag=f" {N}x{K}",
+             work=_gemm_work(M, N, K, a, w, out))
         return out
     lib = load_library("gemm_skinny")
-    _run("gemm_skinny", lib.kp_gemm_skinny, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-         _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
+    _run("gemm_skinny", lib.kp_gemm_skinny_glu if consts else lib.kp_gemm_skinny, _ptr(a), _rows_2d(a, "a"), _ptr(w),
+         _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, epi, *consts, STREAM, tag=f" {N}x{K}",
+         work=_gemm_work(M, N, K, a, w, out))
     return out
 
 

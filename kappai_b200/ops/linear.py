@@ -11,7 +11,7 @@ no library matrix product is called.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -47,17 +47,21 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                  activation: str = "silu") -> torch.Tensor:
-    """``act(a @ Wg.T) * (a @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` and act = silu (or ``activation``); one
-    fused kernel where there is one for the shape, else product then activation.
-    Gate and up are rounded to the storage type before the activation either way."""
+                  activation: str = "silu", glu: Optional[Tuple[float, float, float]] = None) -> torch.Tensor:
+    """``act(a @ Wg.T) * (a @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` and act = silu (or ``activation``); with
+    ``glu`` = (limit, alpha, shift) the gated unit with limits instead, ``g sigmoid(alpha g) (u + shift)`` with
+    ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)``.  One fused kernel where there is one for the
+    shape, else product then activation.  Gate and up are rounded to the storage type before the activation
+    either way."""
     ff = w_gate_up.shape[0] // 2
     act = torch.empty((a.shape[0], ff), dtype=a.dtype, device=a.device)
-    fused = activation in K.FUSED_ACTIVATIONS
+    fused = glu is not None or activation in K.FUSED_ACTIVATIONS
     tc = fused and K.tc_ok(a, w_gate_up)
     if fused and K.skinny_ok(a, w_gate_up) and not (tc and K.tc_pays_for_few_rows(a.shape[0], w_gate_up.shape[0], True)):
-        return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True, activation=activation)
+        return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True, activation=activation, glu=glu)
     if tc:
-        return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True, activation=activation)
+        return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True, activation=activation, glu=glu)
     gu = linear(a, w_gate_up, bias)
+    if glu is not None:
+        return K.glu_clamped(gu, act, *glu)
     return K.swiglu(gu, act, activation)

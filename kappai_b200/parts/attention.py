@@ -266,6 +266,7 @@ class Attention(PagedAttentionKernels, Part):
             s["q_norm.weight"] = WeightSpec((self.dim,), "norm")
             s["k_norm.weight"] = WeightSpec((self.dim,), "norm")
         if self.bias:
+            hd = self.hd                      # (biases go with value_dim = head_dim)
             for n, sz in (("q_proj", H * hd), ("k_proj", G * hd), ("v_proj", G * hd), ("out_proj", d)):
                 s[n + ".bias"] = WeightSpec((sz,), "bias")
         return s

@@ -76,8 +76,9 @@ class SwiGLU(Part):
 
 
 class ClampedGLU(SwiGLU):
-    """``glu_clamped``: see the module's text.  Gate and up run as one product; the unit is computed in float32 from
-    their values in the storage type."""
+    """``glu_clamped``: see the module's text.  Gate and up run as one product whose epilogue computes the unit, in
+    float32 from their values rounded to the storage type (where no product kernel fits the shape, and in float32
+    mode, the product is followed by the row-wise kernel)."""
 
     def __init__(self, params, env):
         Part.__init__(self, params, env)
@@ -91,9 +92,7 @@ class ClampedGLU(SwiGLU):
             raise ConfigError(f"glu_clamped: limit={self.limit} must be positive")
 
     def forward(self, h, residual, ctx):
-        gu = linear(h, self.w_gu, self.b_gu)
-        act = torch.empty((h.shape[0], self.ff), dtype=h.dtype, device=h.device)
-        K.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
+        act = linear_swiglu(h, self.w_gu, self.b_gu, glu=(self.limit, self.alpha, self.shift))
         linear(act, self.w_down, self.b_down, out=residual, accumulate=True)
 
 

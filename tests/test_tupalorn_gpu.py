@@ -335,6 +335,26 @@ def test_norm_over_whole_projections_into_the_cache(H, G, dim, vdim, page, dtype
     assert torch.equal(q2, q_out) and torch.equal(before, cache)
 
 
+@pytest.mark.parametrize("M,K_,ff,limit", [(4, 512, 256, 1.0), (4, 96, 40, 0.5), (100, 128, 64, 3.0), (40, 1024, 512, 7.0), (300, 256, 320, 1.0)])
+def test_clamped_unit_in_the_gated_epilogues_of_the_products(M, K_, ff, limit):
+    """Few rows with K a multiple of 512 stream their weights, other few-row shapes run the register kernel, many rows
+    run tcgen05: all three compute the unit with limits themselves, with biases, and launch no row-wise kernel for it."""
+    from kappai_b200.ops import kernels as K
+    from kappai_b200.ops.linear import linear_swiglu
+    rng = np.random.default_rng(M + ff)
+    a, w = rt(rng.normal(0, 2, (M, K_)), torch.bfloat16), rt(rng.normal(0, 1 / math.sqrt(K_), (2 * ff, K_)), torch.bfloat16)
+    b = rng.normal(0, 0.5, 2 * ff).astype(np.float32).astype(np.float64)
+    before = K.LAUNCHES_BY.get("glu_clamped", 0)
+    got = linear_swiglu(dev(a, torch.bfloat16), dev(w, torch.bfloat16), dev(b), glu=(limit, 1.702, 1.0)).double().cpu().numpy()
+    assert K.LAUNCHES_BY.get("glu_clamped", 0) == before
+    g, u = rt(a @ w[:ff].T + b[:ff], torch.bfloat16), rt(a @ w[ff:].T + b[ff:], torch.bfloat16)
+    g, u = np.minimum(g, limit), np.clip(u, -limit, limit)
+    want = g * P.sigmoid(1.702 * g) * (u + 1.0)
+    assert (g == limit).any() and (u == -limit).any() and (u == limit).any() and (g < limit).any()
+    # (a gate or an up value next to a rounding boundary of the storage type may round the other way: one unit of it)
+    assert np.abs(got - want).max() <= 0.02 * max(1.0, np.abs(want).max())
+
+
 # ------------------------------------------------------------------------------------- the mixers as parts
 
 def _run_part(kind, name, params, local_names, plain_fn, dtype, d, page=16, lens=(300, 70, 33), cuts=(1, 64, 31), tol16=0.05):
