@@ -494,7 +494,9 @@ int kp_lightning_chunks(const void* qkv, int ld, int q_col, int k_col, int v_col
         kp_launch_pdl(lightning_chunk_out_kernel<T, ACT, VEC>, dim3(n_chunks, H, tiles), dim3(LC_THREADS), sm3, s, (const T*)qkv, ld, \
                       q_col, k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, (const float*)scratch, o, ldo, H, dim, vdim, seg_pos, cos_tab, sin_tab, rot, k_scale); \
     } while (0)
-    const bool vec = dtype == KP_DTYPE_BF16 && dim % 8 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && !((uintptr_t)qkv & 15);
+    // (with a rotation whose half is a multiple of 8 the vector staging also fetches cosines and sines 16 bytes at a time)
+    const bool tabs_ok = rot == 0 || (rot / 2) % 8 != 0 || (!((uintptr_t)cos_tab & 15) && !((uintptr_t)sin_tab & 15));
+    const bool vec = dtype == KP_DTYPE_BF16 && dim % 8 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && !((uintptr_t)qkv & 15) && tabs_ok;
     if (vec) {
         if (act == 0) LC3_LAUNCH(bf16, 0, true); else LC3_LAUNCH(bf16, 1, true);
     } else {

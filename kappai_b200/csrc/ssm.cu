@@ -321,8 +321,22 @@ __device__ __forceinline__ void sc_prefix(float* L, const float* __restrict__ da
 }
 
 // A [rows t0 .. t0 + n) x [N] stretch of columns transposed into dst [N][SC_LD] (zeros behind the n rows).
+// vec: the stretch starts on 16 bytes in every row and N is a multiple of 8 (bfloat16 rows): 16 bytes a load.
 template <typename T>
-__device__ __forceinline__ void sc_stage_transposed(float* dst, const T* __restrict__ xbc, int ldx, int col, int N, int t0, int n, int tid) {
+__device__ __forceinline__ void sc_stage_transposed(float* dst, const T* __restrict__ xbc, int ldx, int col, int N, int t0, int n, int tid,
+                                                    bool vec) {
+    if (sizeof(T) == 2 && vec) {
+        const int ng = N / 8;
+        for (int x = tid; x < ng * SC_C; x += SC_THREADS) {
+            const int t = x % SC_C, g = x / SC_C;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (t < n) raw = __ldg(reinterpret_cast<const uint4*>(xbc + (size_t)(t0 + t) * ldx + col + g * 8));
+            const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; e++) dst[(g * 8 + e) * SC_LD + t] = __bfloat162float(e8[e]);
+        }
+        return;
+    }
     for (int x = tid; x < N * SC_C; x += SC_THREADS) {
         const int t = x % SC_C, d = x / SC_C;
         dst[d * SC_LD + t] = t < n ? to_f32(xbc[(size_t)(t0 + t) * ldx + col + d]) : 0.f;
@@ -342,7 +356,7 @@ template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 ssm_chunk_sums_kernel(const T* __restrict__ xbc, int ldx, int b_col, const float* __restrict__ dt, const float* __restrict__ da,
                       const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg, const int* __restrict__ chunk_row0,
-                      float* __restrict__ U, float* __restrict__ cdec, int H, int G, int N, int P) {
+                      float* __restrict__ U, float* __restrict__ cdec, int H, int G, int N, int P, int vec) {
     kp_pdl_begin();
     extern __shared__ __align__(16) float sc_sm[];
     float* Bt = sc_sm;                                           // [N][SC_LD]
@@ -353,7 +367,7 @@ ssm_chunk_sums_kernel(const T* __restrict__ xbc, int ldx, int b_col, const float
     const int grp = head / (H / G);
     const int t0 = chunk_row0[chunk], n = min(SC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
     sc_prefix(L, da, H, head, t0, n, tid);
-    sc_stage_transposed<T>(Bt, xbc, ldx, b_col + grp * N, N, t0, n, tid);
+    sc_stage_transposed<T>(Bt, xbc, ldx, b_col + grp * N, N, t0, n, tid, vec != 0);
     sc_stage_values<T>(Vs, xbc, ldx, head, P, tile, t0, n, tid);
     __syncthreads();
     for (int x = tid; x < SC_C; x += SC_THREADS) kw[x] = x < n ? expf(L[n - 1] - L[x]) * dt[(size_t)(t0 + x) * H + head] : 0.f;
@@ -424,18 +438,56 @@ ssm_chunk_states_kernel(float* __restrict__ U, const float* __restrict__ cdec, f
     if (write_state) *st = S;
 }
 
-// (3) y_i = sum_{j <= i} exp(L_i - L_j) (C_i . B_j) dt_j x_j + exp(L_i) C_i^T S + D x_i, S the state at the chunk's head
+// (0) M[chunk][group][i][j] = C_i . B_j for the 4 x 4 pieces of the chunk that hold a j <= i: the same for all heads of a
+// group and all tiles of their values, so it is computed once.
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
-ssm_chunk_out_kernel(const T* __restrict__ xbc, int ldx, int b_col, int c_col, const float* __restrict__ dt, const float* __restrict__ da,
-                     const float* __restrict__ Dh, const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg,
-                     const int* __restrict__ chunk_row0, const float* __restrict__ U, float* __restrict__ y, int ldy, int H, int G,
-                     int N, int P) {
+ssm_chunk_cb_kernel(const T* __restrict__ xbc, int ldx, int b_col, int c_col, const int* __restrict__ cu_rows,
+                    const int* __restrict__ chunk_seg, const int* __restrict__ chunk_row0, float* __restrict__ M, int G, int N, int vec) {
     kp_pdl_begin();
     extern __shared__ __align__(16) float sc_sm[];
     float* Ct = sc_sm;                                           // [N][SC_LD]
     float* Bt = Ct + (size_t)N * SC_LD;                          // [N][SC_LD]
-    float* Vs = Bt + (size_t)N * SC_LD;                          // [SC_C][SC_COLS]
+    const int chunk = blockIdx.x, grp = blockIdx.y, tid = threadIdx.x;
+    const int t0 = chunk_row0[chunk], n = min(SC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
+    sc_stage_transposed<T>(Ct, xbc, ldx, c_col + grp * N, N, t0, n, tid, vec != 0);
+    sc_stage_transposed<T>(Bt, xbc, ldx, b_col + grp * N, N, t0, n, tid, vec != 0);
+    __syncthreads();
+    const int i0 = (tid / 16) * 4, j0 = (tid % 16) * 4;
+    if (!(j0 <= i0 + 3 && i0 < n)) return;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+#pragma unroll 4
+    for (int d = 0; d < N; d++) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Ct + d * SC_LD + i0);
+        const float4 k4 = *reinterpret_cast<const float4*>(Bt + d * SC_LD + j0);
+        const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
+    }
+    float* Mc = M + ((size_t)chunk * G + grp) * SC_C * SC_C;
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+        *reinterpret_cast<float4*>(Mc + (i0 + a) * SC_C + j0) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+}
+
+// (3) y_i = sum_{j <= i} exp(L_i - L_j) (C_i . B_j) dt_j x_j + exp(L_i) C_i^T S + D x_i, S the state at the chunk's head;
+// the products C_i . B_j come from pass (0)
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+ssm_chunk_out_kernel(const T* __restrict__ xbc, int ldx, int c_col, const float* __restrict__ dt, const float* __restrict__ da,
+                     const float* __restrict__ Dh, const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg,
+                     const int* __restrict__ chunk_row0, const float* __restrict__ U, const float* __restrict__ M, float* __restrict__ y,
+                     int ldy, int H, int G, int N, int P, int vec) {
+    kp_pdl_begin();
+    extern __shared__ __align__(16) float sc_sm[];
+    float* Ct = sc_sm;                                           // [N][SC_LD]
+    float* Vs = Ct + (size_t)N * SC_LD;                          // [SC_C][SC_COLS]
     float* Ps = Vs + SC_C * SC_COLS;                             // [SC_C][SC_LD]
     float* Ss = Ps + SC_C * SC_LD;                               // [N][SC_COLS]
     float* L = Ss + (size_t)N * SC_COLS;                         // [SC_C]
@@ -444,8 +496,7 @@ ssm_chunk_out_kernel(const T* __restrict__ xbc, int ldx, int b_col, int c_col, c
     const int grp = head / (H / G);
     const int t0 = chunk_row0[chunk], n = min(SC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
     sc_prefix(L, da, H, head, t0, n, tid);
-    sc_stage_transposed<T>(Ct, xbc, ldx, c_col + grp * N, N, t0, n, tid);
-    sc_stage_transposed<T>(Bt, xbc, ldx, b_col + grp * N, N, t0, n, tid);
+    sc_stage_transposed<T>(Ct, xbc, ldx, c_col + grp * N, N, t0, n, tid, vec != 0);
     sc_stage_values<T>(Vs, xbc, ldx, head, P, tile, t0, n, tid);
     const float* Sc = U + ((size_t)chunk * H + head) * N * P;
     for (int x = tid; x < N * SC_COLS; x += SC_THREADS) {
@@ -459,31 +510,19 @@ ssm_chunk_out_kernel(const T* __restrict__ xbc, int ldx, int b_col, int c_col, c
     const int i0 = (tid / 16) * 4, j0 = (tid % 16) * 4;
     const int r0 = (tid / 8) * 2, c0 = (tid % 8) * 4;
     {
-        float acc[4][4];
-#pragma unroll
-        for (int a = 0; a < 4; a++)
-#pragma unroll
-            for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
-        if (j0 <= i0 + 3 && i0 < n) {
-#pragma unroll 4
-            for (int d = 0; d < N; d++) {
-                const float4 q4 = *reinterpret_cast<const float4*>(Ct + d * SC_LD + i0);
-                const float4 k4 = *reinterpret_cast<const float4*>(Bt + d * SC_LD + j0);
-                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-                for (int a = 0; a < 4; a++)
-#pragma unroll
-                    for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
-            }
-        }
+        const bool piece = j0 <= i0 + 3 && i0 < n;                // (the pieces that pass (0) wrote)
+        const float* Mc = M + ((size_t)chunk * G + grp) * SC_C * SC_C;
 #pragma unroll
         for (int a = 0; a < 4; a++) {
+            float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (piece) m4 = *reinterpret_cast<const float4*>(Mc + (i0 + a) * SC_C + j0);
+            const float ma[4] = {m4.x, m4.y, m4.z, m4.w};
             float4 out;
             float* po = reinterpret_cast<float*>(&out);
 #pragma unroll
             for (int b = 0; b < 4; b++) {
                 const int i = i0 + a, j = j0 + b;
-                po[b] = (j <= i && i < n) ? acc[a][b] * (expf(L[i] - L[j]) * dts[j]) : 0.f;
+                po[b] = (j <= i && i < n) ? ma[b] * (expf(L[i] - L[j]) * dts[j]) : 0.f;
             }
             *reinterpret_cast<float4*>(Ps + (i0 + a) * SC_LD + j0) = out;
         }
@@ -592,10 +631,14 @@ int kp_ssm_scan(const void* xbc, int ldx, int b_col, int c_col, const float* dt,
 }
 
 int kp_ssm_chunk_rows() { return SC_C; }
+// floats of scratch that kp_ssm_chunks wants: every chunk's sum a head, its decay, and the products C B^T a (chunk, group)
+long long kp_ssm_chunks_scratch(int n_chunks, int H, int G, int N, int P) {
+    return (((long long)n_chunks * H * N * P + (long long)n_chunks * H + 3) / 4) * 4 + (long long)n_chunks * G * SC_C * SC_C;
+}
 
 // The chunked form: the arguments of kp_ssm_scan and the list of chunks (chunk_seg, chunk_row0 [n_chunks]: every chunk's
 // segment, numbered among the n_seg segments given here, and first row; seg_chunk0 [n_seg + 1]: the first chunk of every
-// segment).  scratch: n_chunks * H * (N * P + 1) floats.  KP_ERR_UNSUPPORTED for states it does not take (N > 128).
+// segment).  scratch: kp_ssm_chunks_scratch floats, 16-byte aligned.  KP_ERR_UNSUPPORTED for states it does not take (N > 128).
 int kp_ssm_chunks(const void* xbc, int ldx, int b_col, int c_col, const float* dt, const float* da, const float* Dh, float* state,
                   long long slot_stride, const int* cu_rows, const int* seg_pos, const int* seg_slot, const int* chunk_seg,
                   const int* chunk_row0, const int* seg_chunk0, int n_chunks, float* scratch, float* y, int ldy, int n_seg, int H,
@@ -604,23 +647,32 @@ int kp_ssm_chunks(const void* xbc, int ldx, int b_col, int c_col, const float* d
     if (H < 1 || G < 1 || H % G || N < 1 || P < 1) return KP_ERR_BAD_ARG;
     const int tiles = (P + SC_COLS - 1) / SC_COLS;
     if (N > SC_MAX_N || H > 65535 || tiles > 65535 || (N * P + 255) / 256 > 65535) return KP_ERR_UNSUPPORTED;
+    const size_t sm0 = (size_t)2 * N * SC_LD * sizeof(float);
     const size_t sm1 = ((size_t)N * SC_LD + SC_C * SC_COLS + 2 * SC_C) * sizeof(float);
-    const size_t sm3 = ((size_t)2 * N * SC_LD + SC_C * SC_COLS + SC_C * SC_LD + (size_t)N * SC_COLS + 2 * SC_C) * sizeof(float);
+    const size_t sm3 = ((size_t)N * SC_LD + SC_C * SC_COLS + SC_C * SC_LD + (size_t)N * SC_COLS + 2 * SC_C) * sizeof(float);
     float* U = scratch;
     float* cdec = scratch + (size_t)n_chunks * H * N * P;
+    float* M = scratch + (((size_t)n_chunks * H * N * P + (size_t)n_chunks * H + 3) / 4) * 4;      // (on 16 bytes behind both)
+    const int esz = dtype == KP_DTYPE_F32 ? 4 : 2;
+    const int vec = (esz == 2 && N % 8 == 0 && ldx % 8 == 0 && b_col % 8 == 0 && c_col % 8 == 0 && (uintptr_t)xbc % 16 == 0) ? 1 : 0;
+    if ((uintptr_t)scratch % 16) return KP_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     KP_DISPATCH_DTYPE(dtype, T, {
+        if ((e = cudaFuncSetAttribute(ssm_chunk_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm0)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(ssm_chunk_sums_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(ssm_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e;
+        kp_launch_pdl(ssm_chunk_cb_kernel<T>, dim3(n_chunks, G), dim3(SC_THREADS), sm0, s, (const T*)xbc, ldx, b_col, c_col, cu_rows, chunk_seg,
+                      chunk_row0, M, G, N, vec);
+        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
         kp_launch_pdl(ssm_chunk_sums_kernel<T>, dim3(n_chunks, H, tiles), dim3(SC_THREADS), sm1, s, (const T*)xbc, ldx, b_col, dt, da, cu_rows,
-                      chunk_seg, chunk_row0, U, cdec, H, G, N, P);
+                      chunk_seg, chunk_row0, U, cdec, H, G, N, P, vec);
         if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
         kp_launch_pdl(ssm_chunk_states_kernel, dim3(n_seg, H, (N * P + 255) / 256), dim3(256), 0, s, U, (const float*)cdec, state,
                       (size_t)slot_stride, seg_pos, seg_slot, seg_chunk0, H, N, P, write_state);
         if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-        kp_launch_pdl(ssm_chunk_out_kernel<T>, dim3(n_chunks, H, tiles), dim3(SC_THREADS), sm3, s, (const T*)xbc, ldx, b_col, c_col, dt, da, Dh,
-                      cu_rows, chunk_seg, chunk_row0, (const float*)U, y, ldy, H, G, N, P);
+        kp_launch_pdl(ssm_chunk_out_kernel<T>, dim3(n_chunks, H, tiles), dim3(SC_THREADS), sm3, s, (const T*)xbc, ldx, c_col, dt, da, Dh,
+                      cu_rows, chunk_seg, chunk_row0, (const float*)U, (const float*)M, y, ldy, H, G, N, P, vec);
     });
     return kp_launch_status();
 }

@@ -785,12 +785,14 @@ def ssm_chunks(xbc: torch.Tensor, dt: torch.Tensor, da: torch.Tensor, D: torch.T
         raise KernelError("ssm_chunks: chunk lists too short")
     if N > SSM_CHUNK_MAX_STATE:
         raise KernelError(f"ssm_chunks: state={N} exceeds {SSM_CHUNK_MAX_STATE}")
-    scratch = torch.empty(n_chunks * H * (N * P + 1), dtype=torch.float32, device=xbc.device)
+    lib = load_library("ssm")
+    lib.kp_ssm_chunks_scratch.restype = ctypes.c_longlong
+    scratch = torch.empty(int(lib.kp_ssm_chunks_scratch(int(n_chunks), H, G, N, P)), dtype=torch.float32, device=xbc.device)
     _run("ssm_chunks", load_library("ssm").kp_ssm_chunks, _ptr(xbc), _rows_2d(xbc, "xbc"), H * P, H * P + G * N, _ptr(dt), _ptr(da),
          _ptr(D), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(chunk_seg),
          _ptr(chunk_row0), _ptr(seg_chunk0), int(n_chunks), _ptr(scratch), _ptr(y), _rows_2d(y, "y"), int(n_seg), H, G, N, P,
          int(bool(write_state)), dtype_code(xbc.dtype), STREAM, work=(4 * n * H * N * P, 0))
-    LAUNCHES[0] += 2
+    LAUNCHES[0] += 3
     return y
 
 
