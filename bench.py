@@ -450,12 +450,12 @@ def tupalorn_config(width, H, G, hd, ff):
     and an attention layer that reads its keys and values through a shorter window."""
     ssm = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
     ret = {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-3 - 6 * h / max(1, H - 1)) for h in range(H)],
-           "rot": {"dims": hd, "base": 1000000.0}}
+           "rot": {"dims": hd, "base": 10000.0}}
     att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_BLOCK}}
     mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
     mixers = [("mamba2", ssm), ("retention", ret), ("attention", att),
               ("attention", dict(att, kv_from=2, mask={"size": TUPALORN_WINDOW}))]
-    return {"architecture": "Tupalorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+    return {"architecture": "Tupalorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 50.0,
             "layers": [{"type": t, "mixer": dict(m), "mlp": dict(mlp)} for t, m in mixers]}
 
 

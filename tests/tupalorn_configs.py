@@ -75,11 +75,11 @@ TUP_C = _model(19, 36, [
 # (tensor-core attention kernels) and a window of two pages; a state of 128; prompts of several chunks
 TUP_D = _model(400, 512, [
     _layer(_mamba2(8, 64, 128, 1, 4, 1), 1024, 1.0),
-    _layer(_retention(4, 64, 64, [0.6, 0.9, 0.99, 0.9999], rot=(32, 1.0e6)), 512, 1.0),
+    _layer(_retention(4, 64, 64, [0.6, 0.9, 0.99, 0.9999], rot=(32, 5.0e5)), 512, 1.0),
     _layer(_attention(8, 2, 64, 64, 128), 1024, 4.0),
     _layer(_mamba2(16, 32, 64, 4, 4, 2), 512, 1.0),
     _layer(_attention(8, 2, 64, 64, 40, 0.1, kv_from=2), 512, 1.0),
-], softcap=30.0, max_positions=1024)
+], softcap=25.0, max_positions=1024)
 # E: sixteen query heads on one key head (more than the split-key kernel shares); retention heads of 128 x 64; a
 # state of 200 rows (the scan keeps it, the chunked kernels do not); a convolution of eight taps
 TUP_E = _model(300, 256, [
