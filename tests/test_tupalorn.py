@@ -205,3 +205,20 @@ def test_grouped_norm_and_softcap():
     n = P.grouped_rms_norm(y, np.ones(4), 2, 0.0)
     assert np.allclose(n, [[3 / math.sqrt(12.5), 4 / math.sqrt(12.5), 0.0, math.sqrt(2.0)]])
     assert np.allclose(P.softcap(np.array([0.0, 1e9, -1e9]), 7.0), [0.0, 7.0, -7.0])
+
+
+def test_the_bench_configurations_are_valid_models():
+    """``bench.py --design tupalorn`` times these layer sizes: every one of them reads as a model with one lender and one
+    borrower whose window is shorter than the lender's own."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for name, width, H, G, hd, ff, *_ in bench.DESIGN_SIZES:
+        cfg = bench.tupalorn_config(width, H, G, hd, ff)
+        m = _spec(cfg)
+        assert [l.mixer.kind for l in m.layers] == ["mamba2", "lightning", "attention", "attention"], name
+        assert [e.cache_of for e in m.schedule] == [None, None, None, 2]
+        assert m.layers[2].mixer.params["cache_window"] == bench.DESIGN_BLOCK and m.layers[3].mixer.params["window"] == bench.TUPALORN_WINDOW
