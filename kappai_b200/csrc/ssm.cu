@@ -9,8 +9,8 @@
 // storage type holds the projection and the convolution's output only.  A request keeps, between steps, the state S
 // and the last taps - 1 inputs of the convolution (both float32, in its slot; both count as zero at position 0).
 //
-// Kernels: the convolution (one thread a (row, channel); the same launch computes dt and the decay's logarithm of every
-// (row, head)); the update of the kept inputs (a launch of its own behind it, because rows at a segment's head still
+// Kernels: the convolution (one thread a (row, channel), or 16 bytes of channels of four rows where the rows allow it;
+// the same launch computes dt and the decay's logarithm of every (row, head)); the update of the kept inputs (a launch of its own behind it, because rows at a segment's head still
 // read the old ones; in a step of single-row segments the convolution does it itself); the scan (a block walks the
 // rows of one (segment, head, 16 value columns) with the state in registers, every sum in an order fixed by the sizes
 // alone, so a row's bits do not depend on how the sequence was cut); and the chunked form for prompt portions in 16-bit
@@ -300,9 +300,10 @@ ssm_scan_kernel(const T* __restrict__ xbc, int ldx, int b_col, int c_col, const 
 // from the chunk's first row up to row i, the rows of a chunk are independent given the state S at its head:
 //   y_i = sum_{j <= i} exp(L_i - L_j) (C_i . B_j) dt_j x_j + exp(L_i) C_i^T S + D x_i ,
 //   S'  = exp(L_last) S + sum_j exp(L_last - L_j) dt_j B_j x_j^T ,
-// small float32 matrix products from shared memory.  The chunks of all segments run side by side: (1) every chunk's own
-// sum U_c and its whole decay, (2) a serial pass a (segment, head) that turns the sums into the states at the chunks'
-// heads in place and leaves the last state in the slot, (3) every chunk's outputs.  Every exponent is <= 0.
+// small float32 matrix products from shared memory.  The chunks of all segments run side by side: (0) the products
+// C_i . B_j of every (chunk, group), which all heads of the group share, (1) every chunk's own sum U_c and its whole
+// decay, (2) a serial pass a (segment, head) that turns the sums into the states at the chunks' heads in place and
+// leaves the last state in the slot, (3) every chunk's outputs.  Every exponent is <= 0.
 #define SC_C 64
 #define SC_LD (SC_C + 4)
 #define SC_COLS 32

@@ -775,7 +775,7 @@ def ssm_chunks(xbc: torch.Tensor, dt: torch.Tensor, da: torch.Tensor, D: torch.T
                seg_chunk0: torch.Tensor, n_chunks: int, y: torch.Tensor, n_seg: int, H: int, G: int, N: int, P: int,
                write_state: bool = True) -> torch.Tensor:
     """The recurrence of :func:`ssm_scan` for segments of many rows, chunks of rows as small float32 matrix products,
-    the chunks of all segments side by side (sums, a serial pass over a segment's chunks, outputs).  The chunk lists
+    the chunks of all segments side by side (C B^T a group, sums, a serial pass over a segment's chunks, outputs).  The chunk lists
     as in :func:`lightning_chunks`.  Sums have another order than the scan's."""
     n = _ssm_check("ssm_chunks", xbc, dt, da, D, state, y, H, G, N, P)
     for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot"), (chunk_seg, "chunk_seg"),
