@@ -42,6 +42,8 @@
 #define EPI_STORE_F32 1
 #define EPI_ACCUM_F32 2
 #define EPI_SWIGLU 3
+#define EPI_GLU 4                            // inside this file only: EPI_SWIGLU whose unit is the one with limits (act code 3)
+#define TC_GATED(E) ((E) == EPI_SWIGLU || (E) == EPI_GLU)
 
 #define TC_BM 128
 #define TC_BK 64
@@ -95,17 +97,17 @@ __device__ __forceinline__ void tc_finish(const TcArgs& p, int n_lim, const floa
     for (int j = 0; j < W; j++) {
         float x = g[j];
         if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
-        if (EPI == EPI_SWIGLU) {
+        if TC_GATED(EPI) {
             float up = u[j];
             if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
             // gate and up are rounded to the storage type first, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-            x = kp_gated_epilogue(p.act, gq, uq, p.glu_limit, p.glu_alpha, p.glu_shift);
+            x = EPI == EPI_GLU ? kp_glu_clamped(gq, uq, p.glu_limit, p.glu_alpha, p.glu_shift) : kp_act_epilogue(p.act, gq) * uq;
         }
         v[j] = x;
     }
     const bool whole = p.vec_ok && n_base + W <= n_lim;                  // vector stores of the whole piece
-    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+    if (EPI == EPI_STORE || TC_GATED(EPI)) {
         bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
         if (whole && W >= 8) {
 #pragma unroll
@@ -151,7 +153,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const TcArgs p) {
     constexpr int B_BYTES = BN * TC_BK * 2;
-    constexpr int N_OUT_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;       // output columns of the tile
+    constexpr int N_OUT_TILE = TC_GATED(EPI) ? BN / 2 : BN;       // output columns of the tile
     const int A_BYTES = p.a_rows * TC_BK * 2;                            // the rows of A that are brought in
     const int STAGES = p.n_stages;
     extern __shared__ unsigned char smem[];
@@ -169,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (p.K + TC_BK - 1) / TC_BK;
-    const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+    const int n_out = TC_GATED(EPI) ? p.ff : p.N;
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (n_out + N_OUT_TILE - 1) / N_OUT_TILE;
     const int n_tiles = tiles_m * tiles_n;
     const int S = p.splits;                                              // parts along K; a unit of work is (tile, part)
@@ -198,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             auto load_w = [&](int s, int kb, int n0) {
                 unsigned char* b_dst = tiles + (size_t)s * (A_BYTES + B_BYTES) + A_BYTES;
-                if (EPI == EPI_SWIGLU) {
+                if TC_GATED(EPI) {
                     kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
                     kp_tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
                 } else {
@@ -292,13 +294,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
                     uint32_t r[32], u[32];
                     kp_tmem_ld32(lane_base + c, r);
-                    if (EPI == EPI_SWIGLU) kp_tmem_ld32(lane_base + BN / 2 + c, u);
+                    if TC_GATED(EPI) kp_tmem_ld32(lane_base + BN / 2 + c, u);
                     if (m < p.M) {
                         float g[32], up[32];
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
                             g[j] = __uint_as_float(r[j]);
-                            up[j] = EPI == EPI_SWIGLU ? __uint_as_float(u[j]) : 0.f;
+                            up[j] = TC_GATED(EPI) ? __uint_as_float(u[j]) : 0.f;
                         }
                         tc_finish<EPI, 32>(p, n_out, g, up, m, n0 + c);
                     }
@@ -354,7 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr int NT = TC_EPI_PER_Q * 128;
             // VI float4s a thread at a time, the parts four by four: the loads of a round are all in flight
             // together (each is a trip to another SM), the sums still run in the order of the parts
-            constexpr int VI = EPI == EPI_SWIGLU ? 2 : 4;
+            constexpr int VI = TC_GATED(EPI) ? 2 : 4;
             for (int i0 = lo + (int)threadIdx.x - 64; i0 < hi; i0 += VI * NT) {
                 float4 g[VI], up[VI];
 #pragma unroll
@@ -369,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             t[v][u] = t2[v][u] = make_float4(0.f, 0.f, 0.f, 0.f);
                             if (idx < hi && sp0 + u < S) {
                                 t[v][u] = kp_ld_cluster_f4(mine + (uint32_t)idx * 16, sp0 + u);
-                                if (EPI == EPI_SWIGLU) t2[v][u] = kp_ld_cluster_f4(mine + (uint32_t)idx * 16 + up_off, sp0 + u);
+                                if TC_GATED(EPI) t2[v][u] = kp_ld_cluster_f4(mine + (uint32_t)idx * 16 + up_off, sp0 + u);
                             }
                         }
 #pragma unroll
@@ -472,8 +474,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaSt
     a.n_stages = stages;
     int st = prepare<BN, EPI>(smem);
     if (st) return st;
-    const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
-    const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+    const int n_out = TC_GATED(EPI) ? a.ff : a.N;
+    const int n_tile = TC_GATED(EPI) ? BN / 2 : BN;
     const int n_units = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM) * a.splits;
     const int sms = tc_n_sm();
     cudaLaunchConfig_t cfg = {};
@@ -636,6 +638,13 @@ static int tc_run(const void* A, int lda, const void* W, int ldw, const float* b
         case EPI_STORE_F32: TC_PICK(EPI_STORE_F32)
         case EPI_ACCUM_F32: TC_PICK(EPI_ACCUM_F32)
         case EPI_SWIGLU:
+            if (a.act == KP_ACT_GLU_CLAMPED) {           // an instantiation of its own: the others' epilogues stay as they were
+                switch (bn) {
+                    case 256: return launch<256, EPI_GLU>(ta, tw, a, s);
+                    case 128: return launch<128, EPI_GLU>(ta, tw, a, s);
+                    default: return launch<64, EPI_GLU>(ta, tw, a, s);
+                }
+            }
             switch (bn) {
                 case 256: return launch<256, EPI_SWIGLU>(ta, tw, a, s);
                 case 128: return launch<128, EPI_SWIGLU>(ta, tw, a, s);
