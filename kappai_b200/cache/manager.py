@@ -40,14 +40,18 @@ def _ceil_div(a: int, b: int) -> int:
 class PagePool:
     """Pages of one layer group."""
 
-    def __init__(self, n_pages: int, page_size: int, window: Optional[int] = None, block: Optional[int] = None):
+    def __init__(self, n_pages: int, page_size: int, window: Optional[int] = None, block: Optional[int] = None,
+                 keep_first: int = 0):
         if n_pages < 1 or page_size < 1:
             raise CacheError("a page pool needs at least one page and a positive page size")
         if window is not None and window < 1:
             raise CacheError("window must be positive")
         if block is not None and block < 1:
             raise CacheError("block must be positive")
+        if keep_first < 0:
+            raise CacheError("keep_first must not be negative")
         self.n_pages, self.page_size, self.window, self.block = n_pages, page_size, window, block
+        self.keep_first = int(keep_first)                             # the first keys of a sequence are read for good
         self._free: List[int] = list(range(n_pages - 1, -1, -1))      # stack: lowest page first
         self._tables: Dict[Hashable, List[int]] = {}
         self._held: Dict[Hashable, int] = {}                          # pages currently held per request
@@ -108,7 +112,8 @@ class PagePool:
         """Groups with a window or with blocks of positions: give back pages
         whose every key lies before the window of position ``next_pos`` (the
         next token to run), or before the start of that position's block, and
-        hence out of reach of all later positions too.  Returns the number of
+        hence out of reach of all later positions too.  The pages that hold the
+        first ``keep_first`` keys of the sequence stay.  Returns the number of
         pages released."""
         first_needed = 0
         if self.window is not None:
@@ -119,7 +124,7 @@ class PagePool:
             return 0
         t = self._tables[req]
         n = 0
-        for b in range(min(first_needed // self.page_size, len(t))):
+        for b in range(_ceil_div(self.keep_first, self.page_size), min(first_needed // self.page_size, len(t))):
             if t[b] != RELEASED:
                 self._free.append(t[b])
                 t[b] = RELEASED
@@ -207,8 +212,9 @@ class RequestCache:
 class CacheManager:
     """All page groups and the slot pool of one engine.
 
-    ``groups`` maps a group key to ``(n_pages, page_size, window)`` or
-    ``(n_pages, page_size, window, block)``.  Each
+    ``groups`` maps a group key to ``(n_pages, page_size, window)``,
+    ``(n_pages, page_size, window, block)`` or
+    ``(n_pages, page_size, window, block, keep_first)``.  Each
     request gets one slot (used by every state-holding layer) and one block
     table per group.
     """

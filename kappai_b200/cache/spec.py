@@ -7,7 +7,8 @@ recurrent/conv state of fixed size per layer):
 * :class:`PagedKVSpec` — keys and values that grow with the tokens; kept in
   pages.  Mixers with the same (kv heads, head dim, window) form a *group*
   that shares block tables; groups with different needs have pages of their
-  own.
+  own.  A windowed group may keep the first ``keep_first`` keys of every
+  sequence readable: the pages that hold them are never given back early.
 * :class:`StateSpec` — a fixed-size tensor per request; kept in a slot.
 """
 from __future__ import annotations
@@ -22,12 +23,16 @@ class PagedKVSpec:
     head_dim: int
     window: Optional[int] = None      # keys older than this many positions are never read again
     block: Optional[int] = None       # a position reads no key from before its own block of this many positions
+    keep_first: int = 0               # with a window: the first keys of a sequence stay readable for good
 
     @property
     def group_key(self) -> Tuple:
-        if self.block is None:
-            return ("kv", self.num_kv_heads, self.head_dim, self.window)
-        return ("kv", self.num_kv_heads, self.head_dim, self.window, ("block", self.block))
+        key = ("kv", self.num_kv_heads, self.head_dim, self.window)
+        if self.block is not None:
+            key += (("block", self.block),)
+        if self.keep_first and self.window is not None:
+            key += (("keep_first", self.keep_first),)
+        return key
 
 
 @dataclass(frozen=True)

@@ -134,7 +134,9 @@ class LayerSpec:
     """A block: the arrangement (``block``, with its constants in
     ``block_params``) of a mixer, a feed-forward and the norms it needs.  Chosen
     layer by layer.  ``side`` (category ``side``): something that changes the
-    residual at the layer's end, behind the feed-forward."""
+    residual at the layer's end, behind the feed-forward.  ``mixer_post_norm``
+    / ``ffn_post_norm``: norms of a sublayer's output before it joins the
+    residual, for arrangements that norm on both sides."""
 
     mixer: PartSpec
     ffn: Optional[PartSpec]
@@ -143,6 +145,8 @@ class LayerSpec:
     block: str = "prenorm_residual"
     block_params: Dict[str, Any] = field(default_factory=dict)
     side: Optional[PartSpec] = None
+    mixer_post_norm: Optional[PartSpec] = None
+    ffn_post_norm: Optional[PartSpec] = None
 
 
 @dataclass
@@ -173,6 +177,7 @@ class ModelSpec:
     eos_token_id: Optional[int] = None
     entry: Optional[PartSpec] = None           # category ``entry``: runs in front of schedule entries marked ``enter``
     token_table: Optional[PartSpec] = None     # a second table by token id that the layers' ``side`` parts read
+    ignored_tensors: List[str] = field(default_factory=list)   # names a weight file may hold although nothing reads them
 
     def validate(self) -> None:
         if self.hidden_size < 1 or self.vocab_size < 1:

@@ -3,6 +3,10 @@
 // For the row at position p of a request, head h reads kv head g = h / (H/G)
 // and the keys t in [max(0, p - window + 1), p] (window <= 0: all keys):
 //   s_t = (q . K_t) * scale ;  out = sum_t softmax(s)_t V_t
+// Two variants, each an argument: `keep_first` > 0 lets every row also read the keys 0 .. keep_first - 1 that
+// lie before its window (at their true places: the tiles between them and the window are skipped); `sink`
+// (one float32 number a query head, or null) adds exp(sink_h) to the softmax's denominator, a key that has a
+// score but no value, counted once a row.
 // (src/backend/cpu/scalar/core.c:383-433: online softmax with running max M,
 // sum S and rescaled accumulator).  Keys are found through the request's
 // block table: key t lies in page table[t / page_size] at offset t % page_size
@@ -24,7 +28,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
 attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, T* __restrict__ out, int ldo, float scale, int window,
-                      int page_size, int H, int G, int hd, int block) {
+                      int page_size, int H, int G, int hd, int block, int keep_first, const float* __restrict__ sink) {
     kp_pdl_begin();
     __shared__ float qs[KP_MAX_HEAD_DIM];
     __shared__ float ps[ATT_THREADS];
@@ -37,6 +41,7 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
     int k_lo = window > 0 ? max(0, pos - window + 1) : 0;
     if (block > 0) k_lo = max(k_lo, (pos / block) * block);      // nothing from before the row's own block of positions
     const int k_hi = pos;
+    const int first_hi = min(keep_first, k_lo);                  // keys 0 .. first_hi - 1 are read as well
     const size_t page_stride = (size_t)2 * G * page_size * hd;   // elements per page (K and V)
     const size_t k_off = (size_t)g * page_size * hd;
     const size_t v_off = ((size_t)G + g) * page_size * hd;
@@ -44,11 +49,16 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
     for (int i = tid; i < hd; i += ATT_THREADS) qs[i] = to_f32(q[(size_t)row * ldq + (size_t)h * hd + i]);
     __syncthreads();
 
-    float m = -INFINITY, l = 0.f;
+    // (the sink enters as a key that was seen before all others: maximum sink_h, sum 1, no value)
+    float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
     float acc0 = 0.f, acc1 = 0.f;
-    for (int tile0 = (k_lo / ATT_THREADS) * ATT_THREADS; tile0 <= k_hi; tile0 += ATT_THREADS) {
+    for (int tile0 = first_hi > 0 ? 0 : (k_lo / ATT_THREADS) * ATT_THREADS; tile0 <= k_hi; tile0 += ATT_THREADS) {
+        if (tile0 >= first_hi && tile0 + ATT_THREADS <= k_lo) {  // between the kept keys and the window: on to the window's tile
+            tile0 = (k_lo / ATT_THREADS) * ATT_THREADS - ATT_THREADS;
+            continue;
+        }
         const int key = tile0 + tid;
-        const bool valid = key >= k_lo && key <= k_hi;
+        const bool valid = key <= k_hi && (key >= k_lo || key < first_hi);
         float s = -INFINITY;
         if (valid) {
             const T* kp = cache + (size_t)bt[key / page_size] * page_stride + k_off + (size_t)(key % page_size) * hd;
@@ -66,10 +76,10 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
         __syncthreads();
         acc0 *= corr;
         acc1 *= corr;
-        const int kk_lo = max(k_lo - tile0, 0);
         const int kk_hi = min(k_hi - tile0, ATT_THREADS - 1);
-        for (int kk = kk_lo; kk <= kk_hi; kk++) {
+        for (int kk = 0; kk <= kk_hi; kk++) {
             const int key2 = tile0 + kk;
+            if (key2 < k_lo && key2 >= first_hi) continue;
             const T* vp = cache + (size_t)bt[key2 / page_size] * page_stride + v_off + (size_t)(key2 % page_size) * hd;
             const float pv = ps[kk];
             if (tid < hd) acc0 = fmaf(pv, to_f32(vp[tid]), acc0);
@@ -84,19 +94,29 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
 }
 
 // block: 0, or the size of the blocks of positions (counted from 0) beyond whose start a row reads no keys.
-extern "C" int kp_attention_rows_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                                        const int* row_seg, const int* positions, void* out, int ldo, float scale,
-                                        int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
-                                        void* stream) {
+// keep_first: the first keys of the sequence that stay readable behind a window; sink: [H] float32 or null.
+extern "C" int kp_attention_rows_sink(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                      const int* row_seg, const int* positions, void* out, int ldo, float scale,
+                                      int window, int block, int keep_first, const float* sink, int page_size, int n,
+                                      int H, int G, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && block > 0)) return KP_ERR_BAD_ARG;
     if (hd < 2 || hd > KP_MAX_HEAD_DIM) return KP_ERR_UNSUPPORTED;
     if (G < 1 || H % G != 0 || page_size < 1) return KP_ERR_BAD_ARG;
     if (n > 65535) return KP_ERR_UNSUPPORTED;
     dim3 grid(H, n);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attention_rows_kernel<T>, dim3(grid), dim3(ATT_THREADS), 0, (cudaStream_t)stream, 
         (const T*)q, ldq, (const T*)cache, block_table, max_blocks, row_seg, positions, (T*)out, ldo, scale, window,
-        page_size, H, G, hd, block)));
+        page_size, H, G, hd, block, window > 0 ? keep_first : 0, sink)));
     return kp_launch_status();
+}
+
+extern "C" int kp_attention_rows_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                        const int* row_seg, const int* positions, void* out, int ldo, float scale,
+                                        int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
+                                        void* stream) {
+    return kp_attention_rows_sink(q, ldq, cache, block_table, max_blocks, row_seg, positions, out, ldo, scale, window, block,
+                                  0, nullptr, page_size, n, H, G, hd, dtype, stream);
 }
 
 extern "C" int kp_attention_rows(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,

@@ -10,6 +10,11 @@
 // Scratch (global memory beyond inputs and outputs, given by the caller):
 //   part_acc [n_rows][H][n_chunks][hd] float, part_ml [n_rows][H][n_chunks][2] float.
 // Only the chunks that intersect a row's key range are written and read.
+//
+// Two variants, each an argument.  `keep_first` > 0: behind a window a row also reads the keys 0 .. keep_first - 1
+// of its sequence; the chunks that hold them are computed and merged in front of the window's chunks, the chunks
+// in between are skipped.  `sink` (one float32 number a query head, or null): exp(sink_h) is added to the softmax's
+// denominator, once a row, by the merge (the chunk kernels know nothing of it).
 #include "common.cuh"
 
 #define AD_CHUNK 256
@@ -44,6 +49,13 @@ __device__ __forceinline__ void key_range(int pos, int window, int block, int& k
     if (block > 0) k_lo = max(k_lo, (pos / block) * block);
     k_hi = pos;
 }
+// The chunks a row's merge walks: those that hold kept first keys (keys below first_hi = min(keep_first, k_lo)) and
+// lie before the window's first chunk c_lo, then c_lo .. c_hi.  n_front of the first kind; the i-th of all is
+// chunk_at(i, ...).
+__device__ __forceinline__ int front_chunks(int first_hi, int chunk_keys, int c_lo) {
+    return min(c_lo, (first_hi + chunk_keys - 1) / chunk_keys);
+}
+__device__ __forceinline__ int chunk_at(int i, int n_front, int c_lo) { return i < n_front ? i : c_lo + (i - n_front); }
 
 // HD, RR: head size and query heads per kv head fixed at compile time (loops unroll, loads overlap);
 // 0 means "taken from the arguments".
@@ -52,7 +64,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, const int* __restrict__ block_table,
                   int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
-                  int page_size, int H, int G, int hd_rt, int block) {
+                  int page_size, int H, int G, int hd_rt, int block, int keep_first) {
     kp_pdl_begin();
     extern __shared__ float smem[];
     const int hd = HD ? HD : hd_rt;
@@ -68,7 +80,8 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     int k_lo, k_hi;
     key_range(positions[row], window, block, k_lo, k_hi);
     const int c0 = chunk * AD_CHUNK;
-    if (c0 > k_hi || c0 + AD_CHUNK - 1 < k_lo) return;          // the chunk holds none of this row's keys
+    const int first_hi = min(keep_first, k_lo);                 // keys below it are read although they lie before the window
+    if (c0 > k_hi || (c0 + AD_CHUNK - 1 < k_lo && c0 >= first_hi)) return;          // the chunk holds none of this row's keys
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
     const size_t page_stride = (size_t)2 * G * page_size * hd;
     const size_t k_off = (size_t)g * page_size * hd, v_off = ((size_t)G + g) * page_size * hd;
@@ -87,7 +100,7 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
         for (int j = 0; j < 32; j++) {
             const int key2 = c0 + slice_p * 32 + j;
             uint32_t v = 0;
-            if (key2 >= k_lo && key2 <= k_hi)
+            if (key2 <= k_hi && (key2 >= k_lo || key2 < first_hi))
                 v = *reinterpret_cast<const uint32_t*>(cache + (size_t)bt[key2 / page_size] * page_stride + v_off +
                                                        (size_t)(key2 % page_size) * hd + 2 * pair_p);
             vpre[j] = v;
@@ -96,7 +109,7 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
 
     // scores: one key a thread, all R heads
     const int key = c0 + tid;
-    const bool valid = key >= k_lo && key <= k_hi;
+    const bool valid = key <= k_hi && (key >= k_lo || key < first_hi);
     float s[AD_RMAX];
 #pragma unroll
     for (int r = 0; r < AD_RMAX; r++) s[r] = 0.f;
@@ -179,10 +192,11 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
             }
         }
     } else if (slice < n_slices) {
-        const int kk_lo = max(slice * per, k_lo - c0), kk_hi = min(min((slice + 1) * per, AD_CHUNK) - 1, k_hi - c0);
+        const int kk_lo = max(slice * per, first_hi > c0 ? 0 : k_lo - c0), kk_hi = min(min((slice + 1) * per, AD_CHUNK) - 1, k_hi - c0);
 #pragma unroll 8
         for (int kk = kk_lo; kk <= kk_hi; kk++) {
             const int key2 = c0 + kk;
+            if (key2 < k_lo && key2 >= first_hi) continue;
             const T* vp = cache + (size_t)bt[key2 / page_size] * page_stride + v_off +
                           (size_t)(key2 % page_size) * hd + 2 * pair;
             const float v0 = to_f32(vp[0]), v1 = to_f32(vp[1]);
@@ -228,7 +242,8 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
-                                  int chunk_keys, int window, int H, int hd, int block) {
+                                  int chunk_keys, int window, int H, int hd, int block, int keep_first,
+                                  const float* __restrict__ sink) {
     kp_pdl_begin_early_if(gridDim.y > 1);
     extern __shared__ __align__(16) float merge_sm[];       // [MERGE_BATCH], [n_chunks] l_c, [n_chunks] exp(m_c - m), [32]
     const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
@@ -236,14 +251,15 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     key_range(positions[row], window, block, k_lo, k_hi);
     // (a position beyond the chunks the caller gave is the caller's fault; the clamp keeps the reads inside
     // the scratch and the shared arrays all the same)
-    const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi), n = c_hi - c_lo + 1;
+    const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi);
+    const int n_front = front_chunks(min(keep_first, k_lo), chunk_keys, c_lo), n = n_front + c_hi - c_lo + 1;
     float* s_acc = merge_sm;
     float* s_l = merge_sm + MERGE_BATCH;
     float* s_w = s_l + n_chunks;
     float* s_red = s_w + n_chunks;
     // the accumulators: brought in batches of MERGE_BATCH floats by all threads (every load of a batch in
     // flight at once), then added chunk by chunk by the thread of each dimension
-    const float* pa = part_acc + (((size_t)row * H + h) * n_chunks + c_lo) * hd;
+    const float* pa = part_acc + ((size_t)row * H + h) * n_chunks * hd;
     const int mb = MERGE_BATCH / hd;                        // chunks a batch
     constexpr int PER = MERGE_BATCH / 4 / MERGE_THREADS;    // float4 a thread and batch
     float4 reg[PER];
@@ -252,14 +268,17 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
 #pragma unroll
         for (int k = 0; k < PER; k++) {
             const int i = (k * MERGE_THREADS + tid) * 4;
-            if (i < nb * hd) reg[k] = *reinterpret_cast<const float4*>(pa + (size_t)c0 * hd + i);
+            if (i < nb * hd) {
+                const int j = i / hd;                       // (hd is a multiple of 4: a float4 stays inside one chunk)
+                reg[k] = *reinterpret_cast<const float4*>(pa + (size_t)chunk_at(c0 + j, n_front, c_lo) * hd + (i - j * hd));
+            }
         }
     };
     fetch(0);                                               // under way while the statistics are worked out
-    const float* ml = part_ml + (((size_t)row * H + h) * n_chunks + c_lo) * 2;
+    const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
     float m = -INFINITY;
     for (int c = tid; c < n; c += nt) {
-        const float2 v = *reinterpret_cast<const float2*>(ml + 2 * c);
+        const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(c, n_front, c_lo));
         s_w[c] = v.x;                                       // m_c for now
         s_l[c] = v.y;
         m = fmaxf(m, v.x);
@@ -269,9 +288,10 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     __syncthreads();
     m = -INFINITY;
     for (int w = 0; w < (nt + 31) / 32; w++) m = fmaxf(m, s_red[w]);
+    if (sink) m = fmaxf(m, sink[h]);
     for (int c = tid; c < n; c += nt) s_w[c] = expf(s_w[c] - m);
     __syncthreads();
-    float l = 0.f;
+    float l = sink ? expf(sink[h] - m) : 0.f;               // the sink: in the denominator once, with no value
     for (int c = 0; c < n; c++) l = __fmaf_rn(s_l[c], s_w[c], l);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     float v = 0.f;
@@ -300,7 +320,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
 template <typename T>
 __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
-                                       int chunk_keys, int window, int H, int hd, int n_rows, int block) {
+                                       int chunk_keys, int window, int H, int hd, int n_rows, int block, int keep_first,
+                                       const float* __restrict__ sink) {
     kp_pdl_begin_early_if(n_rows > 1);
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);          // (row, head)
@@ -308,9 +329,10 @@ __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const
     const int row = item / H, h = item - row * H;
     int k_lo, k_hi;
     key_range(positions[row], window, block, k_lo, k_hi);
-    const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi), n = c_hi - c_lo + 1;
-    const float* pa = part_acc + (((size_t)row * H + h) * n_chunks + c_lo) * hd;
-    const float* ml = part_ml + (((size_t)row * H + h) * n_chunks + c_lo) * 2;
+    const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi);
+    const int n_front = front_chunks(min(keep_first, k_lo), chunk_keys, c_lo), n = n_front + c_hi - c_lo + 1;
+    const float* pa = part_acc + ((size_t)row * H + h) * n_chunks * hd;
+    const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
     // the sums of the first MERGE_WARP_BLOCK chunks are on their way while the statistics are worked out
     constexpr int B = MERGE_WARP_BLOCK;
     float a[B][4];
@@ -320,16 +342,17 @@ __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int d = lane + 32 * i;
-                a[j][i] = (c0 + j < n && d < hd) ? pa[(size_t)(c0 + j) * hd + d] : 0.f;
+                a[j][i] = (c0 + j < n && d < hd) ? pa[(size_t)chunk_at(c0 + j, n_front, c_lo) * hd + d] : 0.f;
             }
     };
     fetch(0);
     float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;                       // chunks lane and lane + 32
-    if (lane < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * lane); m0 = v.x; l0 = v.y; }
-    if (lane + 32 < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * (lane + 32)); m1 = v.x; l1 = v.y; }
-    const float m = warp_max(fmaxf(m0, m1));
+    if (lane < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane, n_front, c_lo)); m0 = v.x; l0 = v.y; }
+    if (lane + 32 < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane + 32, n_front, c_lo)); m1 = v.x; l1 = v.y; }
+    float m = warp_max(fmaxf(m0, m1));
+    if (sink) m = fmaxf(m, sink[h]);
     const float w0 = lane < n ? expf(m0 - m) : 0.f, w1 = lane + 32 < n ? expf(m1 - m) : 0.f;
-    float l = 0.f, v[4] = {0.f, 0.f, 0.f, 0.f};
+    float l = sink ? expf(sink[h] - m) : 0.f, v[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c0 = 0; c0 < n; c0 += B) {
         if (c0) fetch(c0);
 #pragma unroll
@@ -356,11 +379,13 @@ static size_t merge_smem_bytes(int n_chunks) { return sizeof(float) * ((size_t)2
 
 template <typename T>
 static int launch_merge(const float* part_acc, const float* part_ml, const int* positions, void* out, int ldo,
-                        int n_chunks, int chunk_keys, int window, int block, int n, int H, int hd, cudaStream_t s) {
+                        int n_chunks, int chunk_keys, int window, int block, int keep_first, const float* sink, int n, int H,
+                        int hd, cudaStream_t s) {
+    if (window <= 0) keep_first = 0;
     if (n_chunks <= MERGE_WARP_CHUNKS && hd <= 128) {
         const int warps = 8;
         kp_launch_pdl(attn_merge_warp_kernel<T>, dim3((n * H + warps - 1) / warps), dim3(warps * 32), 0, s, part_acc, part_ml,
-                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n, block);
+                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n, block, keep_first, sink);
         return kp_launch_status();
     }
     const size_t smem = merge_smem_bytes(n_chunks);
@@ -371,7 +396,7 @@ static int launch_merge(const float* part_acc, const float* part_ml, const int* 
     }
     if (hd > MERGE_THREADS || (hd & 3)) return KP_ERR_UNSUPPORTED;
     kp_launch_pdl(attn_merge_kernel<T>, dim3(H, n), dim3(MERGE_THREADS), smem, s, part_acc, part_ml, positions, (T*)out, ldo,
-                  n_chunks, chunk_keys, window, H, hd, block);
+                  n_chunks, chunk_keys, window, H, hd, block, keep_first, sink);
     return kp_launch_status();
 }
 
@@ -390,11 +415,14 @@ long long kp_attention_split_scratch(int n_rows, int H, int hd, int n_chunks) {
 
 // n_chunks: chunks of 256 keys the grid covers; must reach the largest position in the batch.
 // block: 0, or the size of the blocks of positions that a row's keys do not reach beyond (see key_range).
-int kp_attention_split_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                              const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
-                              float scale, int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
-                              void* stream) {
+// keep_first: the first keys of the sequence that stay readable behind a window; sink: [H] float32 or null.
+int kp_attention_split_sink(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                            const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
+                            float scale, int window, int block, int keep_first, const float* sink, int page_size, int n,
+                            int H, int G, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && block > 0)) return KP_ERR_BAD_ARG;
+    if (window <= 0) keep_first = 0;
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || (hd & 15)) return KP_ERR_UNSUPPORTED;
     if (G < 1 || H % G != 0 || H / G > AD_RMAX || page_size < 1 || n_chunks < 1) return KP_ERR_UNSUPPORTED;
     if (n > 65535 || G > 65535) return KP_ERR_UNSUPPORTED;
@@ -407,7 +435,7 @@ int kp_attention_split_masked(const void* q, int ldq, const void* cache, const i
 #define AD_LAUNCH(T, HD, RR)                                                                                      \
     kp_launch_pdl(attn_split_kernel<T, HD, RR>, dim3(grid), dim3(AD_THREADS), smem, s, (const T*)q, ldq, (const T*)cache, block_table,       \
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
-                                                                n_chunks, scale, window, page_size, H, G, hd, block)
+                                                                n_chunks, scale, window, page_size, H, G, hd, block, keep_first)
     KP_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e0;
         if (hd == 64 && R == 4) e0 = AD_LAUNCH(T, 64, 4);
@@ -415,10 +443,18 @@ int kp_attention_split_masked(const void* q, int ldq, const void* cache, const i
         else if (hd == 128) e0 = AD_LAUNCH(T, 128, 0);
         else e0 = AD_LAUNCH(T, 0, 0);
         if (e0 != cudaSuccess) { cudaGetLastError(); return (int)e0; }      // the first launch that failed
-        return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, AD_CHUNK, window, block, n, H, hd, s);
+        return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, AD_CHUNK, window, block, keep_first, sink, n, H, hd, s);
     });
 #undef AD_LAUNCH
     return kp_launch_status();
+}
+
+int kp_attention_split_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                              const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
+                              float scale, int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
+                              void* stream) {
+    return kp_attention_split_sink(q, ldq, cache, block_table, max_blocks, row_seg, positions, out, ldo, scratch, n_chunks,
+                                   scale, window, block, 0, nullptr, page_size, n, H, G, hd, dtype, stream);
 }
 
 int kp_attention_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
@@ -430,15 +466,22 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
 
 // The merge alone, for partials of chunks of `chunk_keys` keys that another kernel wrote into `scratch` in the
 // same format.
-int kp_attention_merge_masked(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
-                              int chunk_keys, int window, int block, int n, int H, int hd, int dtype, void* stream) {
+int kp_attention_merge_sink(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
+                            int chunk_keys, int window, int block, int keep_first, const float* sink, int n, int H, int hd,
+                            int dtype, void* stream) {
     if (n <= 0) return 0;
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535 || chunk_keys < 1) return KP_ERR_UNSUPPORTED;
     const float* part_acc = scratch;
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     KP_DISPATCH_DTYPE(dtype, T, return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, chunk_keys, window,
-                                                       block, n, H, hd, (cudaStream_t)stream));
+                                                       block, keep_first, sink, n, H, hd, (cudaStream_t)stream));
     return kp_launch_status();
+}
+
+int kp_attention_merge_masked(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
+                              int chunk_keys, int window, int block, int n, int H, int hd, int dtype, void* stream) {
+    return kp_attention_merge_sink(positions, out, ldo, scratch, n_chunks, chunk_keys, window, block, 0, nullptr, n, H, hd,
+                                   dtype, stream);
 }
 
 int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int chunk_keys,

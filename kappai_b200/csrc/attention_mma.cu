@@ -78,16 +78,17 @@ __device__ __forceinline__ bf16* tile_chunk(bf16* tile, int r, int c) {
     return tile + (size_t)(c >> 3) * (AM_TILE * 64) + (size_t)r * 64 + (((c & 7) ^ (r & 7)) << 3);
 }
 
-// Bring keys [k0, k0+64) of one kv head into a K tile and a V tile.  Keys outside [k_lo, k_hi] are zero-filled.
+// Bring keys [k0, k0+64) of one kv head into a K tile and a V tile.  Keys outside [k_lo, k_hi] are zero-filled,
+// except the first `keep` keys of the sequence, which are read wherever the window stands.
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(bf16* Kt, bf16* Vt, const bf16* __restrict__ cache, const int* __restrict__ bt,
                                              size_t page_stride, size_t k_off, size_t v_off, int page_size, int k0,
-                                             int k_lo, int k_hi, int tid, int nthreads) {
+                                             int k_lo, int k_hi, int tid, int nthreads, int keep = 0) {
     constexpr int CPR = HD / 8;                      // 16-byte chunks a row
     for (int i = tid; i < AM_TILE * CPR; i += nthreads) {
         const int r = i / CPR, c = i % CPR;
         const int key = k0 + r;
-        const bool valid = key >= k_lo && key <= k_hi;
+        const bool valid = key <= k_hi && (key >= k_lo || key < keep);
         const bf16* src = cache;
         if (valid) src = cache + (size_t)bt[key / page_size] * page_stride + (size_t)(key % page_size) * HD + c * 8;
         cp_async16(tile_chunk<HD>(Kt, r, c), src + (valid ? k_off : 0), valid);
@@ -583,13 +584,17 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
 
 // ------------------------------------------------------------------ prefill (segments of many rows)
 // One CTA: 64 consecutive rows (tile `qt` of segment `seg`) of one head.  tile_seg / tile_q0 list the tiles.
+// keep_first > 0: the rows also read the first keep_first keys of the sequence behind their windows; the key tiles
+// that hold them come first, then the tiles of the window, the tiles in between are left out.  sink (one float32 a
+// query head, or null): a row's running maximum and sum start at (sink_h, 1) instead of (-inf, 0), which is a key
+// with that score and no value.
 template <int HD, bool EXACT>
 __global__ void __launch_bounds__(128)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_rows,
                         const int* __restrict__ seg_pos, const int* __restrict__ tile_seg,
                         const int* __restrict__ tile_row0, bf16* __restrict__ out, int ldo, float scale, int window,
-                        int page_size, int H, int G, int block) {
+                        int page_size, int H, int G, int block, int keep_first, const float* __restrict__ sink) {
     constexpr bool exact_p = EXACT;
     kp_pdl_begin();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -611,6 +616,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
     const int k_hi_all = pos0 + n_rows - 1;
     const int k_lo_all = kp_key_lo(pos0, window, block);
     const int tile_lo = k_lo_all / AM_TILE, tile_hi = k_hi_all / AM_TILE;
+    const int n_front = keep_first > 0 ? min(tile_lo, (keep_first + AM_TILE - 1) / AM_TILE) : 0;   // tiles of kept first keys
+    const int n_kt = n_front + tile_hi - tile_lo + 1;
 
     // this warp's 16 rows: rows r0 = warp*16 + g and r0 + 8
     const int ra = warp * 16 + g, rb = ra + 8;
@@ -635,16 +642,19 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
     for (int dn = 0; dn < HD / 8; dn++)
 #pragma unroll
         for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
-    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const float m_start = sink ? sink[h] : -INFINITY, l_start = sink ? 1.f : 0.f;
+    float m_a = m_start, m_b = m_start, l_a = l_start, l_b = l_start;
 
-    load_kv_tile<HD>(Ks, Vs, cache, bt, page_stride, k_off, v_off, page_size, tile_lo * AM_TILE, k_lo_all, k_hi_all,
-                     tid, 128);
+    load_kv_tile<HD>(Ks, Vs, cache, bt, page_stride, k_off, v_off, page_size, (n_front ? 0 : tile_lo) * AM_TILE, k_lo_all, k_hi_all,
+                     tid, 128, keep_first);
     cp_async_commit();
-    for (int kt = tile_lo; kt <= tile_hi; kt++) {
-        const int buf = (kt - tile_lo) & 1;
-        if (kt + 1 <= tile_hi) {
+    for (int it = 0; it < n_kt; it++) {
+        const int kt = it < n_front ? it : tile_lo + (it - n_front);
+        const int buf = it & 1;
+        if (it + 1 < n_kt) {
+            const int kt_next = it + 1 < n_front ? it + 1 : tile_lo + (it + 1 - n_front);
             load_kv_tile<HD>(Ks + (buf ^ 1) * AM_TILE * HD, Vs + (buf ^ 1) * AM_TILE * HD, cache, bt, page_stride, k_off,
-                             v_off, page_size, (kt + 1) * AM_TILE, k_lo_all, k_hi_all, tid, 128);
+                             v_off, page_size, kt_next * AM_TILE, k_lo_all, k_hi_all, tid, 128, keep_first);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -655,7 +665,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
         // a warp whose rows all lie before this tile (causal) or after its window has nothing to do in it
         const int w_pos_hi = pos0 + min(warp * 16 + 15, n_rows - 1);
         const int w_lo = kp_key_lo(pos0 + warp * 16, window, block);
-        if (warp * 16 < n_rows && t0 <= w_pos_hi && t0 + AM_TILE - 1 >= w_lo) {
+        if (warp * 16 < n_rows && t0 <= w_pos_hi && (t0 + AM_TILE - 1 >= w_lo || t0 < keep_first)) {
             float s[8][4];
             qk_tile<HD>(s, qf, Ks + buf * AM_TILE * HD, lane);
             float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -664,8 +674,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const int key = t0 + nt * 8 + 2 * t + i;
-                    const float va = (has_a && key <= pos_a && key >= lo_a) ? s[nt][i] * scale : -INFINITY;
-                    const float vb = (has_b && key <= pos_b && key >= lo_b) ? s[nt][2 + i] * scale : -INFINITY;
+                    const float va = (has_a && key <= pos_a && (key >= lo_a || key < keep_first)) ? s[nt][i] * scale : -INFINITY;
+                    const float vb = (has_b && key <= pos_b && (key >= lo_b || key < keep_first)) ? s[nt][2 + i] * scale : -INFINITY;
                     s[nt][i] = va; s[nt][2 + i] = vb;
                     mx_a = fmaxf(mx_a, va); mx_b = fmaxf(mx_b, vb);
                 }
@@ -788,14 +798,15 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
 template <int HD>
 static int launch_prefill(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
                           const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0, int n_tiles,
-                          void* out, int ldo, float scale, int window, int block, int exact_p, int page_size, int H, int G, cudaStream_t s) {
+                          void* out, int ldo, float scale, int window, int block, int keep_first, const float* sink, int exact_p,
+                          int page_size, int H, int G, cudaStream_t s) {
     const size_t smem = (size_t)4 * AM_TILE * HD * 2;
     auto kern = exact_p ? attn_prefill_mma_kernel<HD, true> : attn_prefill_mma_kernel<HD, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     kp_launch_pdl(kern, dim3(dim3(n_tiles, H)), dim3(128), smem, s, 
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-        (bf16*)out, ldo, scale, window, page_size, H, G, block);
+        (bf16*)out, ldo, scale, window, page_size, H, G, block, window > 0 ? keep_first : 0, sink);
     return kp_launch_status();
 }
 
@@ -840,19 +851,28 @@ int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long 
 // tile_seg / tile_row0: for each tile of 64 rows its segment and its first row (device arrays, n_tiles long)
 // block: 0, or the size of the blocks of positions beyond whose start a row reads no key.  exact_p: 1 takes the
 // softmax weights into the product with V whole (three bfloat16 parts), 0 rounded to bfloat16.
-int kp_attention_prefill_mma_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                                    const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
-                                    int n_tiles, void* out, int ldo, float scale, int window, int block, int exact_p,
-                                    int page_size, int H, int G, int hd, void* stream) {
+// keep_first: the first keys of the sequence that stay readable behind a window; sink: [H] float32 or null.
+int kp_attention_prefill_mma_sink(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                  const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
+                                  int n_tiles, void* out, int ldo, float scale, int window, int block, int keep_first,
+                                  const float* sink, int exact_p, int page_size, int H, int G, int hd, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (block < 0) return KP_ERR_BAD_ARG;
+    if (block < 0 || keep_first < 0 || (keep_first > 0 && block > 0)) return KP_ERR_BAD_ARG;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || page_size < 1 || H > 65535 || (ldq & 1) || (ldo & 1))
         return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return launch_prefill<64>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-                                            n_tiles, out, ldo, scale, window, block, exact_p, page_size, H, G, s);
+                                            n_tiles, out, ldo, scale, window, block, keep_first, sink, exact_p, page_size, H, G, s);
     return launch_prefill<128>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
-                               out, ldo, scale, window, block, exact_p, page_size, H, G, s);
+                               out, ldo, scale, window, block, keep_first, sink, exact_p, page_size, H, G, s);
+}
+
+int kp_attention_prefill_mma_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                    const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
+                                    int n_tiles, void* out, int ldo, float scale, int window, int block, int exact_p,
+                                    int page_size, int H, int G, int hd, void* stream) {
+    return kp_attention_prefill_mma_sink(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
+                                         out, ldo, scale, window, block, 0, nullptr, exact_p, page_size, H, G, hd, stream);
 }
 
 int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,

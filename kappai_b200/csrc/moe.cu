@@ -10,6 +10,13 @@
 // constant, not renormalised.  The last `n_identity` router outputs may stand for experts without weights that
 // return their input: their pairs get places in the layout but no tiles, and the combine adds weight * h for them.
 //
+// A third (`mode` 2): the `top` largest logits are chosen, as in the first, and the weight of a chosen expert is
+// sigmoid(z) times the constant, each on its own, not renormalised.
+//
+// The weight may multiply the expert's input instead of its output (`weight_input`): out[r, :] += sum_j unit_e(w_j h_r).
+// The rows are then gathered place by place with their weights applied (float32 product, rounded to the storage
+// type), the grouped products read the gathered rows, and the combine adds the outputs as they are.
+//
 // Which rows meet which expert is known on the device only, so the work is laid out there too and nothing
 // comes back to the host (a step with this layer can be captured in a CUDA graph):
 //   moe_route:  one warp a row picks the experts and their weights;
@@ -73,6 +80,13 @@ __device__ __forceinline__ void moe_choose(float* z, float* s, int E, int top, i
         if (lane < top) {
             idx_out[lane] = my_e;
             w_out[lane] = s[my_e] * wscale;
+        }
+        return;
+    }
+    if (mode == 2) {
+        if (lane < top) {
+            idx_out[lane] = my_e;
+            w_out[lane] = wscale / (1.0f + expf(-my_z));
         }
         return;
     }
@@ -229,7 +243,7 @@ moe_gate_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_gu,
     if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
     const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
     const int n0 = blockIdx.x * BN;
-    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? perm[row0 + tid] / top : -1;
+    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? (perm ? perm[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
     const T* wg = w_gu + (size_t)e * 2 * ff * d;
     const T* wu = wg + (size_t)ff * d;
@@ -407,7 +421,7 @@ moe_gate_up_tc_kernel(const bf16* __restrict__ h, int ldh, const bf16* __restric
     if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * MOE_TC_BN;
-    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? perm[row0 + tid] / top : -1;
+    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? (perm ? perm[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
     const bf16* wg = w_gu + (size_t)e * 2 * ff * d;
     const bf16* wu = wg + (size_t)ff * d;
@@ -672,6 +686,38 @@ __global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, int ldh, cons
     }
 }
 
+// hs[place, :] = weight of the pair at that place * h[its row, :], the product in float32, rounded to the storage type.
+template <typename T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ h, int ldh, const int* __restrict__ perm, const float* __restrict__ w,
+                                         T* __restrict__ hs, int n_pairs, int d, int top) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n_pairs * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t place = i / d, c = i % d;
+        const int pair = perm[place];
+        hs[i] = from_f32<T>(w[pair] * to_f32(h[(size_t)(pair / top) * ldh + c]));
+    }
+}
+// The same for bfloat16 rows of a multiple of 8 columns that start on 16 bytes: 16 bytes a thread and turn.
+__global__ void moe_gather_scaled_vec_kernel(const bf16* __restrict__ h, int ldh, const int* __restrict__ perm,
+                                             const float* __restrict__ w, bf16* __restrict__ hs, int n_pairs, int d8, int top) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n_pairs * d8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t place = i / d8, c = (i % d8) * 8;
+        const int pair = perm[place];
+        const float wt = w[pair];
+        uint4 v = *reinterpret_cast<const uint4*>(h + (size_t)(pair / top) * ldh + c);
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __bfloat1622float2(p2[j]);
+            p2[j] = __floats2bfloat162_rn(wt * f.x, wt * f.y);
+        }
+        *reinterpret_cast<uint4*>(hs + place * (size_t)d8 * 8 + c) = v;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- combine
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ w,
                                    float* __restrict__ out, int n, int d, int top) {
@@ -680,7 +726,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / d, c = i % d;
         float s = 0.f;
-        for (int j = 0; j < top; j++) s = fmaf(w[r * top + j], y[(size_t)inv[r * top + j] * d + c], s);
+        for (int j = 0; j < top; j++) s = fmaf(w ? w[r * top + j] : 1.f, y[(size_t)inv[r * top + j] * d + c], s);   // (no weights: they were applied to the inputs)
         out[i] += s;
     }
 }
@@ -721,11 +767,11 @@ int kp_moe_max_tiles(int n, int E, int top) {
 
 // logits [n, E] float32 -> idx [n, top], weights [n, top], and the layout (see kp_moe_layout_ints).
 // mode 0: the largest logits (+ bias), weights = softmax over the chosen; mode 1: scores = softmax over all, the largest
-// score + bias chosen, weights = score * wscale.  The last n_identity of the E outputs are experts without weights.
+// score + bias chosen, weights = score * wscale; mode 2: the largest logits, weights = sigmoid(logit) * wscale.  The last n_identity of the E outputs are experts without weights.
 int kp_moe_route(const float* logits, const float* bias, int n, int E, int top, int mode, float wscale, int n_identity,
                  int* idx, float* weights, int* layout, void* stream) {
     if (n <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 1 || n_identity < 0 || n_identity >= E)
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 2 || n_identity < 0 || n_identity >= E)
         return KP_ERR_UNSUPPORTED;
     const size_t route_sm = (size_t)8 * 2 * E * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
     if (route_sm > 96 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;            // (E <= 1536)
@@ -753,7 +799,7 @@ int kp_moe_route(const float* logits, const float* bias, int n, int E, int top, 
 int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, int n, int E, int d, int top, int mode,
                   float wscale, int n_identity, int* idx, float* weights, int* layout, int dtype, void* stream) {
     if (n <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 1 || n_identity < 0 || n_identity >= E)
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 2 || n_identity < 0 || n_identity >= E)
         return KP_ERR_UNSUPPORTED;
     const size_t sort_sm = ((size_t)3 * E + 1) * sizeof(int);
     // eight rows a block where there are many and they fit shared memory, else one
@@ -788,10 +834,12 @@ int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, in
 // hs: scratch [n top, d] in the storage type for the tcgen05 path (null: that path is not taken).
 // E counts all router outputs; the last n_identity of them are experts without weights (w_gu and w_down hold
 // E - n_identity experts), for which `idx` [n, top] (the chosen experts) must be given.
-int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
-                   void* act, float* y, float* out, void* hs, int n, int E, int top, int d, int ff, int act_kind, int dtype,
-                   int n_identity, const int* idx, void* stream) {
+// weight_input: the weights multiply the experts' inputs (hs is then needed whatever the path; no identity experts).
+int kp_moe_experts_weighted(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
+                            void* act, float* y, float* out, void* hs, int n, int E, int top, int d, int ff, int act_kind, int dtype,
+                            int n_identity, const int* idx, int weight_input, void* stream) {
     if (n <= 0) return 0;
+    if (weight_input && (hs == nullptr || n_identity > 0)) return KP_ERR_BAD_ARG;
     if (E < 1 || top < 1 || d < 1 || ff < 1 || act_kind < 0 || act_kind > KP_ACT_GELU_TANH) return KP_ERR_BAD_ARG;
     if (n_identity < 0 || n_identity >= E || (n_identity > 0 && idx == nullptr)) return KP_ERR_BAD_ARG;
     const int E_real = E - n_identity;
@@ -805,8 +853,27 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
     const int* inv = perm + (size_t)n * top;
     cudaError_t e0;
     const bool tc = dtype == KP_DTYPE_BF16 && d % 8 == 0 && ff % 8 == 0 && ldh % 8 == 0 &&
-                    !(((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) & 15);
+                    !(((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) & 15) &&
+                    !(weight_input && ((uintptr_t)hs & 15));
     const long long pairs = (long long)n * top;
+    const void* rows = h;                          // what the grouped products of the smaller tiles read, and how
+    int ld_rows = ldh;
+    const int* perm_rows = perm;
+    bool gathered = false;
+    if (weight_input) {
+        size_t gg = ((size_t)pairs * (tc ? d / 8 : d) + 255) / 256;
+        if (gg > 148 * 16) gg = 148 * 16;
+        if (tc) {
+            kp_launch_pdl(moe_gather_scaled_vec_kernel, dim3((unsigned)gg), dim3(256), 0, s, (const bf16*)h, ldh, perm, weights,
+                          (bf16*)hs, (int)pairs, d / 8, top);
+        } else {
+            KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_gather_scaled_kernel<T>, dim3((unsigned)gg), dim3(256), 0, s, (const T*)h,
+                                                       ldh, perm, weights, (T*)hs, (int)pairs, d, top)));
+        }
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        rows = hs; ld_rows = d; perm_rows = nullptr; gathered = true;
+        weights = nullptr;
+    }
     const long long big_tiles = pairs / MOE_BIG + (pairs < E ? pairs : E);
     if (tc && hs != nullptr && pairs >= g_moe_tc_min_pairs && big_tiles <= 65535 && !((uintptr_t)hs & 15) &&
         (long long)E_real * 2 * ff < 2147483647LL && (long long)E_real * d < 2147483647LL) {
@@ -826,9 +893,11 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
         }
         size_t gg = ((size_t)pairs * (d / 8) + 255) / 256;
         if (gg > 148 * 16) gg = 148 * 16;
-        kp_launch_pdl(moe_gather_rows_kernel, dim3((unsigned)gg), dim3(256), 0, s, (const bf16*)h, ldh, perm, (bf16*)hs, (int)pairs,
-                      d / 8, top);
-        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        if (!gathered) {
+            kp_launch_pdl(moe_gather_rows_kernel, dim3((unsigned)gg), dim3(256), 0, s, (const bf16*)h, ldh, perm, (bf16*)hs, (int)pairs,
+                          d / 8, top);
+            if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        }
         MtArgs a1 = {offsets, big_start, E, d, ff, 2 * ff, ff, act, ff, act_kind};
         kp_launch_pdl(moe_tc_kernel<true>, dim3((ff + MT_BN / 2 - 1) / (MT_BN / 2), (unsigned)big_tiles), dim3(MT_THREADS), smem, s,
                       ta1, tw1, a1);
@@ -837,15 +906,15 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
         kp_launch_pdl(moe_tc_kernel<false>, dim3((d + MT_BN - 1) / MT_BN, (unsigned)big_tiles), dim3(MT_THREADS), smem, s, ta2, tw2, a2);
         if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
     } else if (tc) {
-        kp_launch_pdl(moe_gate_up_tc_kernel, dim3((ff + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)h,
-                      ldh, (const bf16*)w_gu, offsets, tile_start, perm, (bf16*)act, E, top, d, ff, act_kind);
+        kp_launch_pdl(moe_gate_up_tc_kernel, dim3((ff + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)rows,
+                      ld_rows, (const bf16*)w_gu, offsets, tile_start, perm_rows, (bf16*)act, E, top, d, ff, act_kind);
         if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
         kp_launch_pdl(moe_down_tc_kernel, dim3((d + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)act,
                       (const bf16*)w_down, offsets, tile_start, y, E, d, ff);
         if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
     } else {
         KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_gate_up_kernel<T>, dim3((ff + 31) / 32, max_tiles), dim3(256), 0, s,
-                                                   (const T*)h, ldh, (const T*)w_gu, offsets, tile_start, perm, (T*)act, E, top,
+                                                   (const T*)rows, ld_rows, (const T*)w_gu, offsets, tile_start, perm_rows, (T*)act, E, top,
                                                    d, ff, act_kind)));
         if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
         KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_down_kernel<T>, dim3((d + 63) / 64, max_tiles), dim3(256), 0, s,
@@ -861,6 +930,13 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
     }
     kp_launch_pdl(moe_combine_kernel, dim3((unsigned)g), dim3(256), 0, s, (const float*)y, inv, weights, out, n, d, top);
     return kp_launch_status();
+}
+
+int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
+                   void* act, float* y, float* out, void* hs, int n, int E, int top, int d, int ff, int act_kind, int dtype,
+                   int n_identity, const int* idx, void* stream) {
+    return kp_moe_experts_weighted(h, ldh, w_gu, w_down, layout, weights, act, y, out, hs, n, E, top, d, ff, act_kind, dtype,
+                                   n_identity, idx, 0, stream);
 }
 
 }  // extern "C"

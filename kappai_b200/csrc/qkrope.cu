@@ -13,9 +13,16 @@
 // Norm (w == nullptr) and rotation (cos_tab == nullptr) can each be left out.
 // With q_out == nullptr, q and k are normed/rotated in place and nothing is
 // written to the cache (for a position encoding applied between two calls).
+// `norm_dim` (<= hd): the number the norm's mean is taken over, for heads stored wider than they are with
+// zeros behind their own columns.  A query temperature (temp_every > 0): the query heads of the row at position
+// p leave multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), computed in float32.
 #include "common.cuh"
 
 #define KP_MAX_HEAD_DIM 256
+
+__device__ __forceinline__ float kp_query_temperature(int pos, float coef, float every) {
+    return 1.0f + coef * logf(floorf((float)(pos + 1) / every) + 1.0f);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -24,7 +31,7 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
                        const float* __restrict__ sin_tab, int rot, int interleaved,
                        const int* __restrict__ positions, const int* __restrict__ slot_map,
                        T* q_out, int ldq, T* __restrict__ cache, int page_size,
-                       int H, int G, int hd, int write_kv, int v_col) {
+                       int H, int G, int hd, int write_kv, int v_col, int norm_dim, float temp_coef, float temp_every) {
     kp_pdl_begin();
     __shared__ float buf[4][KP_MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,7 +55,7 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
     const float* w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
     if (w) {
         ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        const float scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
         for (int i = lane; i < hd; i += 32) x[i] = (x[i] * scale) * w[i];
     }
     __syncwarp();
@@ -64,6 +71,10 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
             x[ib] = a * s + b * c;
         }
         __syncwarp();
+    }
+    if (kind == 0 && temp_every > 0.f) {
+        const float tq = kp_query_temperature(positions[row], temp_coef, temp_every);
+        for (int i = lane; i < hd; i += 32) x[i] *= tq;
     }
     T* dst;
     if (in_place) {
@@ -91,7 +102,8 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
                            const float* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                            const float* __restrict__ sin_tab, const int* __restrict__ positions,
                            const int* __restrict__ slot_map, bf16* __restrict__ q_out, int ldq,
-                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv, int v_col, int rot) {
+                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv, int v_col, int rot,
+                           int norm_dim, float temp_coef, float temp_every) {
     kp_pdl_begin_early();
     constexpr int L = HD / 8;                          // lanes a head
     constexpr int HPB = 128 / L;                       // heads a block
@@ -116,7 +128,7 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
         for (int i = 0; i < 8; i++) ss = fmaf(x[i], x[i], ss);
 #pragma unroll
         for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+        const float scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
         const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + lane_in * 8));
         const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + lane_in * 8) + 1);
         const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -139,6 +151,11 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
         }
     }
     if (!live || (kind != 0 && !write_kv)) return;
+    if (kind == 0 && temp_every > 0.f) {
+        const float tq = kp_query_temperature(positions[row], temp_coef, temp_every);
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] *= tq;
+    }
     uint4 o;
     {
         __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -158,12 +175,14 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
     *reinterpret_cast<uint4*>(dst + lane_in * 8) = o;
 }
 
-extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, const float* k_w, float eps,
-                                  const float* cos_tab, const float* sin_tab, int rot, int interleaved,
-                                  const int* positions, const int* slot_map, void* q_out, int ldq, void* cache,
-                                  int page_size, int n, int H, int G, int hd, int write_kv, int v_col, int dtype,
-                                  void* stream) {
+extern "C" int kp_qk_norm_rope_kv_temp(const void* qkv, int ld, const float* q_w, const float* k_w, float eps,
+                                       const float* cos_tab, const float* sin_tab, int rot, int interleaved,
+                                       const int* positions, const int* slot_map, void* q_out, int ldq, void* cache,
+                                       int page_size, int n, int H, int G, int hd, int write_kv, int v_col, int norm_dim,
+                                       float temp_coef, float temp_every, int dtype, void* stream) {
     if (n <= 0) return 0;
+    if (norm_dim <= 0) norm_dim = hd;
+    if (norm_dim > hd || temp_every < 0.f) return KP_ERR_BAD_ARG;
     if (v_col < 0) v_col = (H + G) * hd;
     if (hd < 2 || hd > KP_MAX_HEAD_DIM || (hd & 1)) return KP_ERR_UNSUPPORTED;
     if (cos_tab && (rot < 2 || rot > hd || (rot & 1))) return KP_ERR_BAD_ARG;
@@ -179,17 +198,28 @@ extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, con
         dim3 vgrid((H + 2 * G + hpb - 1) / hpb, n);
         if (hd == 64)
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<64>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot,
+                          norm_dim, temp_coef, temp_every);
         else
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<128>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot,
+                          norm_dim, temp_coef, temp_every);
         return kp_launch_status();
     }
     dim3 grid((H + 2 * G + 3) / 4, n);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)qkv, ld, q_w, k_w, eps, cos_tab, sin_tab, rot, interleaved, positions, slot_map, (T*)q_out, ldq,
-        (T*)cache, page_size, H, G, hd, write_kv, v_col)));
+        (T*)cache, page_size, H, G, hd, write_kv, v_col, norm_dim, temp_coef, temp_every)));
     return kp_launch_status();
+}
+
+extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, const float* k_w, float eps,
+                                  const float* cos_tab, const float* sin_tab, int rot, int interleaved,
+                                  const int* positions, const int* slot_map, void* q_out, int ldq, void* cache,
+                                  int page_size, int n, int H, int G, int hd, int write_kv, int v_col, int dtype,
+                                  void* stream) {
+    return kp_qk_norm_rope_kv_temp(qkv, ld, q_w, k_w, eps, cos_tab, sin_tab, rot, interleaved, positions, slot_map, q_out, ldq,
+                                   cache, page_size, n, H, G, hd, write_kv, v_col, hd, 0.f, 0.f, dtype, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------

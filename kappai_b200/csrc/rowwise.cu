@@ -378,6 +378,71 @@ rmsnorm_add_rows_kernel(const float* __restrict__ y, const float* __restrict__ w
     for (int i = threadIdx.x; i < d; i += blockDim.x) x[(size_t)r * d + i] += (src[i] * scale) * w[i];
 }
 
+// A branch that is normed before it joins the residual, for layers that norm a sublayer on both sides:
+//   x[r, :] += norm(y[r, :]) * wb ;  y[r, :] = 0 ;  and, if h_out is given, h_out[r, :] = norm(x[r, :]) * wn
+// (the new x; h_out in the storage type: what the sublayer after this one reads).  All statistics float32 with a
+// fixed tree; the branch is cleared for whoever adds into it next.  Rows of at most 256 * RMS_ADD_KEEP floats stay
+// in registers between the passes, longer ones are read again.
+#define RMS_ADD_KEEP 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_norm_rows_kernel(float* __restrict__ y, const float* __restrict__ wb, float eps_b, float* __restrict__ x,
+                             const float* __restrict__ wn, float eps_n, T* __restrict__ h_out, int d) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float* yr = y + (size_t)r * d;
+    float* xr = x + (size_t)r * d;
+    const bool keep = d <= 256 * RMS_ADD_KEEP;
+    float v[RMS_ADD_KEEP];
+    float ss = 0.f;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < RMS_ADD_KEEP; j++) {
+            const int i = threadIdx.x + j * 256;
+            v[j] = i < d ? yr[i] : 0.f;
+            ss = fmaf(v[j], v[j], ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += 256) { const float a = yr[i]; ss = fmaf(a, a, ss); }
+    }
+    ss = block_sum(ss, red);
+    const float sb = 1.0f / sqrtf(ss / (float)d + eps_b);
+    float s2 = 0.f;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < RMS_ADD_KEEP; j++) {
+            const int i = threadIdx.x + j * 256;
+            if (i < d) {
+                v[j] = xr[i] + (v[j] * sb) * wb[i];
+                xr[i] = v[j];
+                yr[i] = 0.f;
+                s2 = fmaf(v[j], v[j], s2);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += 256) {
+            const float a = xr[i] + (yr[i] * sb) * wb[i];
+            xr[i] = a;
+            yr[i] = 0.f;
+            s2 = fmaf(a, a, s2);
+        }
+    }
+    if (h_out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float sn = 1.0f / sqrtf(s2 / (float)d + eps_n);
+    T* hr = h_out + (size_t)r * d;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < RMS_ADD_KEEP; j++) {
+            const int i = threadIdx.x + j * 256;
+            if (i < d) hr[i] = from_f32<T>((v[j] * sn) * wn[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += 256) hr[i] = from_f32<T>((xr[i] * sn) * wn[i]);
+    }
+}
+
 // out[r, :] += sigmoid(h[r, :] . wg) * y[r, :]: a branch weighed by one gate a row, the gate's logit computed here
 // (float32 sum in a fixed order, h widened from its storage type).
 template <typename T>
@@ -775,6 +840,16 @@ int kp_rmsnorm_add_rows(const float* y, const float* w, float* x, int n, int d, 
     if (n <= 0) return 0;
     if (d < 1) return KP_ERR_BAD_ARG;
     kp_launch_pdl(rmsnorm_add_rows_kernel, dim3(n), dim3(256), 0, (cudaStream_t)stream, y, w, x, d, eps);
+    return kp_launch_status();
+}
+
+// wn / h_out: both given or both null.  dtype: the type of h_out.
+int kp_rmsnorm_add_norm_rows(float* y, const float* wb, float eps_b, float* x, const float* wn, float eps_n, void* h_out, int n,
+                             int d, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1 || ((wn == nullptr) != (h_out == nullptr))) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, y, wb,
+                                               eps_b, x, wn, eps_n, (T*)h_out, d)));
     return kp_launch_status();
 }
 

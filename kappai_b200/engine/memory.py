@@ -29,6 +29,7 @@ class GroupNeed:
     key: Hashable
     bytes_per_token: int
     window: Optional[int] = None
+    keep_first: int = 0                  # keys at the head of every sequence that a windowed group never gives back
 
 
 @dataclass
@@ -47,10 +48,10 @@ def _ceil_div(a: int, b: int) -> int:
 
 def pages_of_group(g: GroupNeed, n_pages: int, page_size: int, n_slots: int, max_step_tokens: Optional[int]) -> int:
     """A windowed group never holds more than the window, the portion being run and the page both ends
-    straddle for each request: a full pool for it would lie unused."""
+    straddle for each request, and the pages of the first keys that it keeps: a full pool for it would lie unused."""
     if g.window is None or max_step_tokens is None:
         return n_pages
-    per_request = _ceil_div(g.window + max_step_tokens, page_size) + 1
+    per_request = _ceil_div(g.window + max_step_tokens, page_size) + 1 + _ceil_div(g.keep_first, page_size)
     return max(1, min(n_pages, n_slots * per_request))
 
 

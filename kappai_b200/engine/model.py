@@ -32,9 +32,15 @@ class Model:
             n1 = self._make("norm", ls.mixer_norm) if ls.mixer_norm is not None else None
             n2 = self._make("norm", ls.ffn_norm) if ls.ffn_norm is not None else None
             side = self._make("side", ls.side) if ls.side is not None else None
+            p1 = self._make("norm", ls.mixer_post_norm) if ls.mixer_post_norm is not None else None
+            p2 = self._make("norm", ls.ffn_post_norm) if ls.ffn_post_norm is not None else None
             block = make_part("block", PartSpec(ls.block, dict(ls.block_params)), env)
-            # (an arrangement registered from outside may not know of side parts: it is asked only where there is one)
-            self.blocks.append(block.assemble(mixer, ffn, n1, n2, side) if side is not None else block.assemble(mixer, ffn, n1, n2))
+            # (an arrangement registered from outside may not know of side parts or of norms behind the sublayers: it is
+            # asked only where there is one)
+            if p1 is not None or p2 is not None:
+                self.blocks.append(block.assemble(mixer, ffn, n1, n2, side, post_norms=(p1, p2)))
+            else:
+                self.blocks.append(block.assemble(mixer, ffn, n1, n2, side) if side is not None else block.assemble(mixer, ffn, n1, n2))
         self.final_norm = self._make("norm", spec.final_norm) if spec.final_norm is not None else None
         self.head = self._make("head", spec.head)
         self.schedule = list(spec.schedule)
@@ -42,7 +48,8 @@ class Model:
         self.token_table = self._make("embedding", spec.token_table) if spec.token_table is not None else None
         parts = [self.embedding, self.final_norm, self.head, self.entry, self.token_table]
         for b in self.blocks:
-            parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm, getattr(b, "side", None)]
+            parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm, getattr(b, "side", None),
+                      getattr(b, "mixer_post_norm", None), getattr(b, "ffn_post_norm", None)]
         # a decode step may be captured in a CUDA graph only if every part reads its tables from the device
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts if p is not None)
         # parts that build tables of their own for every step, one builder per key
@@ -123,6 +130,9 @@ class Model:
         for i, e in enumerate(self.schedule):
             if e.enter:
                 x = self.entry.forward(x, h0)
+            # (the block that runs next on this residual, for arrangements that prepare its input in their last kernel)
+            nxt = self.schedule[i + 1] if i + 1 < len(self.schedule) else None
+            ctx.next_block = self.blocks[nxt.layer] if nxt is not None and not nxt.enter else None
             self.blocks[e.layer].forward(x, ctx, cache_views[i])
             if observer is not None:
                 observer(i, x)

@@ -95,7 +95,7 @@ class ModelRunner:
         state_bytes = 0
         for s in specs:
             if isinstance(s, PagedKVSpec):
-                g = needs.setdefault(s.group_key, GroupNeed(s.group_key, 0, s.window))
+                g = needs.setdefault(s.group_key, GroupNeed(s.group_key, 0, s.window, s.keep_first if s.window is not None else 0))
                 g.bytes_per_token += 2 * s.num_kv_heads * s.head_dim * elt
             elif isinstance(s, StateSpec):
                 n = 1
@@ -112,7 +112,9 @@ class ModelRunner:
         group_keys = list(needs)
         self.storage = CacheStorage(specs, borrowing, plan.pages, page_size, max_requests, self.dtype, self.device)
         self.cache = CacheManager({gk: (plan.pages[gk], page_size, self.storage.groups[gk].window,
-                                        self.storage.groups[gk].block) for gk in group_keys}, max_requests)
+                                        self.storage.groups[gk].block,
+                                        self.storage.groups[gk].keep_first if self.storage.groups[gk].window is not None else 0)
+                                   for gk in group_keys}, max_requests)
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
         self.last_h2d_bytes = 0

@@ -498,6 +498,28 @@ def rmsnorm_add_rows(y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tens
     return x
 
 
+def rmsnorm_add_norm_rows(y: torch.Tensor, w_branch: torch.Tensor, eps_branch: float, x: torch.Tensor,
+                          w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0,
+                          h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += rmsnorm(y) * w_branch (float32), y cleared; with ``w_next`` and ``h_out`` also
+    ``h_out = rmsnorm(x) * w_next`` of the new x, in ``h_out``'s type: the norms behind one sublayer and in front
+    of the next in one launch."""
+    _need(y, "y", torch.float32); _need(w_branch, "w_branch", torch.float32); _need(x, "x", torch.float32)
+    n, d = x.shape
+    if tuple(y.shape) != (n, d) or w_branch.numel() != d or (w_next is None) != (h_out is None):
+        raise KernelError("rmsnorm_add_norm_rows: shape mismatch")
+    if n > MAX_STEP_ROWS:
+        raise KernelError("rmsnorm_add_norm_rows: too many rows")
+    if h_out is not None:
+        _need(w_next, "w_next", torch.float32); _need(h_out, "h_out")
+        if tuple(h_out.shape) != (n, d) or w_next.numel() != d:
+            raise KernelError("rmsnorm_add_norm_rows: shape mismatch")
+    _run("rmsnorm_add_norm_rows", load_library("rowwise").kp_rmsnorm_add_norm_rows, _ptr(y), _ptr(w_branch),
+         ctypes.c_float(eps_branch), _ptr(x), _ptr(w_next), ctypes.c_float(eps_next), _ptr(h_out), n, d,
+         dtype_code(h_out.dtype if h_out is not None else torch.float32), STREAM)
+    return x
+
+
 def row_gate_add(h: torch.Tensor, w_gate: torch.Tensor, y: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] += sigmoid(h[r] . w_gate) * y[r]: ``w_gate`` float32 [d], ``y`` and ``out`` float32 [n, d]."""
     _need(h, "h", contiguous=False); _need(w_gate, "w_gate", torch.float32); _need(y, "y", torch.float32)
@@ -802,13 +824,16 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
                     cos_tab: Optional[torch.Tensor], sin_tab: Optional[torch.Tensor], rotary_dim: int,
                     interleaved: bool, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
                     q_out: Optional[torch.Tensor], cache: Optional[torch.Tensor], page_size: int, H: int, G: int,
-                    hd: int, v_col: Optional[int] = None) -> Optional[torch.Tensor]:
+                    hd: int, v_col: Optional[int] = None, norm_dim: Optional[int] = None,
+                    q_temp: Optional[Tuple[float, float]] = None) -> Optional[torch.Tensor]:
     """Norm + rotate q and k; write q to ``q_out`` and, if ``cache`` is given,
     k and v to their pages.  ``cache`` is one layer's [pages, 2, G, page_size, hd].
     With ``q_out`` None, q and k are changed in place and no cache is written.
     ``v_col``: the column of a row at which the values start (default: behind the keys, ``(H + G) * hd``;
     ``H * hd`` makes the values the key projections themselves, before norm and rotation).  Columns behind
-    q, k and v are left alone."""
+    q, k and v are left alone.  ``norm_dim``: the number the norm's mean is taken over where a head is stored
+    wider than it is (zeros behind its own columns; default ``hd``).  ``q_temp`` = (coef, every): the queries of
+    the row at position p leave multiplied by ``1 + coef ln(floor((p + 1) / every) + 1)`` (float32)."""
     _need(qkv, "qkv", contiguous=False)
     _need(positions, "positions", torch.int32)
     n = qkv.shape[0]
@@ -838,12 +863,19 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
         _need(cache, "cache", qkv.dtype); _need(slot_map, "slot_map", torch.int32)
         if tuple(cache.shape[1:]) != (2, G, page_size, hd):
             raise KernelError(f"qk_norm_rope_kv: cache layout {tuple(cache.shape)}")
+    nd = hd if norm_dim is None else int(norm_dim)
+    if not (1 <= nd <= hd):
+        raise KernelError("qk_norm_rope_kv: norm_dim")
+    coef, every = (0.0, 0.0) if q_temp is None else (float(q_temp[0]), float(q_temp[1]))
+    if q_temp is not None and not every > 0:
+        raise KernelError("qk_norm_rope_kv: the query temperature's period must be positive")
     lib = load_library("qkrope")
-    _run("qk_norm_rope_kv", lib.kp_qk_norm_rope_kv, _ptr(qkv), _rows_2d(qkv, "qkv"), _ptr(q_w), _ptr(k_w), ctypes.c_float(eps),
+    _run("qk_norm_rope_kv", lib.kp_qk_norm_rope_kv_temp, _ptr(qkv), _rows_2d(qkv, "qkv"), _ptr(q_w), _ptr(k_w), ctypes.c_float(eps),
                                   _ptr(cos_tab), _ptr(sin_tab), rotary_dim, int(interleaved), _ptr(positions),
                                   _ptr(slot_map), _ptr(q_out), 0 if q_out is None else _rows_2d(q_out, "q_out"), _ptr(cache),
                                   page_size,
-                                  n, H, G, hd, int(write_kv), int(v_col), dtype_code(qkv.dtype), STREAM)
+                                  n, H, G, hd, int(write_kv), int(v_col), nd, ctypes.c_float(coef), ctypes.c_float(every),
+                                  dtype_code(qkv.dtype), STREAM)
     return q_out
 
 
@@ -874,20 +906,33 @@ def qk_rownorm_kv(qkv: torch.Tensor, k_col: int, v_col: int, q_w: torch.Tensor, 
     return q_out
 
 
+def _check_sink(sink: Optional[torch.Tensor], H: int, keep_first: int, window: Optional[int], block: Optional[int], what: str) -> None:
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+        if sink.numel() != H:
+            raise KernelError(f"{what}: one sink a query head")
+    if keep_first and (keep_first < 0 or block):
+        raise KernelError(f"{what}: keep_first must not be negative and does not go with blocks of positions")
+
+
 def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                    positions: torch.Tensor, out: torch.Tensor, scale: float, window: Optional[int],
-                   page_size: int, H: int, G: int, hd: int, block: Optional[int] = None) -> torch.Tensor:
-    """``block``: a row reads no key from before the start of its own block of that many positions."""
+                   page_size: int, H: int, G: int, hd: int, block: Optional[int] = None, keep_first: int = 0,
+                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``block``: a row reads no key from before the start of its own block of that many positions.
+    ``keep_first``: behind its window a row still reads the first that many keys of its sequence.  ``sink``
+    (float32 [H]): ``exp(sink_h)`` joins the softmax's denominator, a key with a score and no value."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32)
     n = q.shape[0]
     if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
         raise KernelError("attention_rows: shape mismatch")
+    _check_sink(sink, H, keep_first, window, block, "attention_rows")
     lib = load_library("attention")
-    _run("attention_rows", lib.kp_attention_rows_masked, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
+    _run("attention_rows", lib.kp_attention_rows_sink, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
          block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
-         int(window or 0), int(block or 0), page_size, n, H, G, hd, dtype_code(q.dtype), STREAM)
+         int(window or 0), int(block or 0), int(keep_first or 0), _ptr(sink), page_size, n, H, G, hd, dtype_code(q.dtype), STREAM)
     return out
 
 
@@ -904,12 +949,15 @@ def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
                     window: Optional[int], page_size: int, H: int, G: int, hd: int,
-                    block: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
+                    block: Optional[int] = None, exact_weights: bool = False, keep_first: int = 0,
+                    sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
     must cover the largest position of the batch; ``scratch`` is float32.
     ``block``: a row reads no key from before the start of its own block of that many positions.
     ``exact_weights``: the softmax weights enter the product with V whole (the scalar kernel always does so; the
-    tensor-core form then multiplies their three bfloat16 parts one after the other) instead of rounded to bfloat16."""
+    tensor-core form then multiplies their three bfloat16 parts one after the other) instead of rounded to bfloat16.
+    ``keep_first`` / ``sink``: as in :func:`attention_rows`; the sink enters in the merge, once a row; kept first
+    keys behind a window take the scalar chunk kernel."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
@@ -918,8 +966,10 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
         raise KernelError("attention_split: shape mismatch")
     if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
         raise KernelError("attention_split: scratch too small")
+    _check_sink(sink, H, keep_first, window, block, "attention_split")
+    keep_first = int(keep_first or 0) if window else 0
     lib = load_library("attention_decode")
-    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
+    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0 and not keep_first:
         # tensor-core chunk pass over smaller chunks, then the same merge
         parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
         _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma_masked,
@@ -927,12 +977,12 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), int(block or 0),
             int(bool(exact_weights)), page_size, n, H, G, hd, STREAM)
-        _run("attention_merge", lib.kp_attention_merge_masked, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
-             parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), n, H, hd, dtype_code(q.dtype), STREAM)
+        _run("attention_merge", lib.kp_attention_merge_sink, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
+             parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), 0, _ptr(sink), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
-    _run("attention_split", lib.kp_attention_split_masked, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
+    _run("attention_split", lib.kp_attention_split_sink, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
          block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
-         n_chunks, ctypes.c_float(scale), int(window or 0), int(block or 0), page_size, n, H, G, hd,
+         n_chunks, ctypes.c_float(scale), int(window or 0), int(block or 0), keep_first, _ptr(sink), page_size, n, H, G, hd,
          dtype_code(q.dtype), STREAM)
     LAUNCHES[0] += 1
     return out
@@ -963,14 +1013,16 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
                       seg_pos: torch.Tensor, tile_seg: torch.Tensor, tile_row0: torch.Tensor, out: torch.Tensor,
                       scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int,
                       big_tile_seg: Optional[torch.Tensor] = None, big_tile_row0: Optional[torch.Tensor] = None,
-                      block: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
+                      block: Optional[int] = None, exact_weights: bool = False, keep_first: int = 0,
+                      sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core causal attention for segments of many rows.  ``tile_seg`` / ``tile_row0`` list, for every
     tile of 64 consecutive rows of a segment, its segment and its first row; ``big_tile_seg`` /
     ``big_tile_row0`` the same for tiles of 128 rows, the tile that reads the most keys first (with them the
     tcgen05 kernel runs where it takes the sizes).  ``block``: a row reads no key from before the start of its own
     block of that many positions.  ``exact_weights``: the softmax weights enter the product with V whole, as three
     bfloat16 parts multiplied one after the other (the mma.sync kernel; the tcgen05 kernel, whose weights pass
-    through shared memory as one bfloat16 operand, is then not taken)."""
+    through shared memory as one bfloat16 operand, is then not taken).  ``keep_first`` / ``sink``: as in
+    :func:`attention_rows` (the mma.sync kernel has them, the tcgen05 kernel is then not taken)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(cache, "cache", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
     for t_, nm in ((block_table, "block_table"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (tile_seg, "tile_seg"),
@@ -981,7 +1033,10 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         raise KernelError("attention_prefill: shape mismatch")
     if tile_seg.numel() != tile_row0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
-    if big_tile_seg is not None and not exact_weights and attention_prefill_tc_ok(q, out, cache, page_size, hd):
+    _check_sink(sink, H, keep_first, window, block, "attention_prefill")
+    keep_first = int(keep_first or 0) if window else 0
+    if (big_tile_seg is not None and not exact_weights and not keep_first and sink is None
+            and attention_prefill_tc_ok(q, out, cache, page_size, hd)):
         _need(big_tile_seg, "big_tile_seg", torch.int32); _need(big_tile_row0, "big_tile_row0", torch.int32)
         if big_tile_seg.numel() != big_tile_row0.numel():
             raise KernelError("attention_prefill: tile lists differ in length")
@@ -992,10 +1047,10 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
             _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), int(block or 0), page_size, H, G, hd,
             STREAM)
         return out
-    _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma_masked,
+    _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma_sink,
         _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
         _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
-        int(window or 0), int(block or 0), int(bool(exact_weights)), page_size, H, G, hd, STREAM)
+        int(window or 0), int(block or 0), keep_first, _ptr(sink), int(bool(exact_weights)), page_size, H, G, hd, STREAM)
     return out
 
 
@@ -1217,7 +1272,7 @@ def moe_layout_ints(n: int, E: int, top: int) -> int:
     return 3 * (E + 1) + 2 * n * top
 
 
-MOE_ROUTINGS = {"top_logits": 0, "softmax_all": 1}
+MOE_ROUTINGS = {"top_logits": 0, "softmax_all": 1, "sigmoid": 2}
 
 
 def _moe_routing(routing: str) -> int:
@@ -1235,7 +1290,8 @@ def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.
     layout of the (row, choice) pairs by expert (``layout``, int32, :func:`moe_layout_ints` words), which the
     grouped products read.  Nothing returns to the host.  ``routing`` ``top_logits``: the largest logits (+ ``bias``),
     weighted by the softmax over the chosen logits alone; ``softmax_all``: scores = softmax over all E outputs, the
-    largest score + ``bias`` are chosen and weighted by their score times ``scale``.  The last ``n_identity``
+    largest score + ``bias`` are chosen and weighted by their score times ``scale``; ``sigmoid``: the largest logits
+    are chosen and each weighted by its own ``sigmoid(logit)`` times ``scale``.  The last ``n_identity``
     outputs stand for experts without weights (places in the layout, no tiles)."""
     _need(logits, "logits", torch.float32); _need(idx, "idx", torch.int32); _need(weights, "weights", torch.float32)
     _need(layout, "layout", torch.int32)
@@ -1296,12 +1352,14 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Ten
 
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, layout: torch.Tensor,
                 weights: torch.Tensor, top: int, out: torch.Tensor, activation: str = "silu", n_identity: int = 0,
-                idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+                idx: Optional[torch.Tensor] = None, weight_input: bool = False) -> torch.Tensor:
     """out[r] += sum_j weights[r, j] * Wd_e (act(Wg_e h[r]) * (Wu_e h[r])), e = the j-th expert of row r as laid out
     by :func:`moe_route`.  ``w_gate_up``: [E, 2 ff, d] (gate rows, then up rows); ``w_down``: [E, d, ff]; ``out``
     float32 [n, d].  bfloat16 operands run on the tensor cores, float32 ones on the CUDA cores in true 32-bit.
     With ``n_identity`` the router had that many outputs more than there are experts here; a pair that chose one of
-    them (``idx`` [n, top] says so) adds ``weight * h[r]``."""
+    them (``idx`` [n, top] says so) adds ``weight * h[r]``.  ``weight_input``: the weight multiplies the unit's
+    input instead, ``out[r] += sum_j Wd_e (act(Wg_e w_j h[r]) * (Wu_e w_j h[r]))`` (the product ``w_j h[r]`` in
+    float32, rounded to the storage type as a matrix operand)."""
     _need(h, "h", contiguous=False); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
     _need(layout, "layout", torch.int32); _need(weights, "weights", torch.float32); _need(out, "out", torch.float32)
     n, d = h.shape
@@ -1316,13 +1374,16 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         _need(idx, "idx", torch.int32)
         if idx.numel() != n * top:
             raise KernelError("moe_experts: idx size")
+        if weight_input:
+            raise KernelError("moe_experts: weights on the inputs do not go with identity experts")
     act = torch.empty((n * top, ff), dtype=h.dtype, device=h.device)
     y = torch.empty((n * top, d), dtype=torch.float32, device=h.device)
     # (many rows, 16-bit: the tcgen05 tiles read the rows laid out place by place)
-    hs = torch.empty((n * top, d), dtype=h.dtype, device=h.device) if (h.dtype == torch.bfloat16 and n * top >= MOE_TC_MIN_PAIRS[0]) else None
-    _run("moe_experts", load_library("moe").kp_moe_experts, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate_up), _ptr(w_down), _ptr(layout),
+    hs = (torch.empty((n * top, d), dtype=h.dtype, device=h.device)
+          if (weight_input or (h.dtype == torch.bfloat16 and n * top >= MOE_TC_MIN_PAIRS[0])) else None)
+    _run("moe_experts", load_library("moe").kp_moe_experts_weighted, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate_up), _ptr(w_down), _ptr(layout),
          _ptr(weights), _ptr(act), _ptr(y), _ptr(out), _ptr(hs), n, E, top, d, ff, activation_code(activation), dtype_code(h.dtype),
-         int(n_identity), _ptr(idx if n_identity else None), STREAM, tag=f" {E}x{ff}x{d}",
+         int(n_identity), _ptr(idx if n_identity else None), int(bool(weight_input)), STREAM, tag=f" {E}x{ff}x{d}",
          work=(6 * n * top * ff * d, min(E, n * top) * 3 * ff * d * h.element_size()))     # (bytes: the experts a step can touch)
     LAUNCHES[0] += 2
     return out

@@ -34,12 +34,20 @@ cache: its schedule entry names the entry whose cache its queries read (after
 that entry's key norm).  ``cache_window``: how many positions back the cache
 must keep keys (at least ``window``; larger where a borrower's window is).
 
+Three more, for designs without a rotation: ``keep_first`` (with a ``window``): the first that many keys of a
+sequence stay visible to every later row, at their true places, and their pages are never given back;
+``sink`` = ``"zero"`` adds one to the softmax's denominator (a key whose score is 0 and which has no value),
+``"learned"`` adds ``exp(sink_h)`` of a tensor ``sink`` [num_heads] (not scaled, counted once a row);
+``q_temp`` = {coef, every}: the query of position p is multiplied by
+``1 + coef ln(floor((p + 1) / every) + 1)`` (float32, in the fused q/k kernel).  The per-head q/k norm goes with a
+``value_dim`` of its own: the norm's mean is then taken over ``head_dim`` columns of the wider cache head.
+
 Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
 value_dim, scale, qk_norm_eps (None: no q/k norm), qk_norm ("per_head" |
 "projection"), window (None: all keys), cache_window, block (None), values
 ("projection" | "keys"), kv ("own" | "borrowed"), gate (None | "sigmoid" |
 "head_sigmoid"), softmax_weights ("operand" | "float32"), position (a
-``position`` PartSpec), bias.
+``position`` PartSpec), bias, keep_first, sink (None | "zero" | "learned"), q_temp.
 """
 from __future__ import annotations
 
@@ -104,7 +112,32 @@ def attention_tiles(segs, split_ok: bool = True):
 class PagedAttentionKernels:
     """The choice among the attention kernels over the paged cache, shared by the mixers that keep keys and values
     there.  The mixer has ``H``, ``G``, ``hd``, ``scale``, ``window``, ``block``, ``exact_weights``, ``split_ok``
-    and ``step_tables_key``."""
+    and ``step_tables_key``; ``keep_first`` and ``sink_w`` (float32 [H] or None) if it has kept first keys or a sink."""
+
+    keep_first = 0
+    sink_w = None
+
+    def _read_sink(self, what: str):
+        """The parameters ``sink`` and ``keep_first`` (shared by the mixers over the paged cache)."""
+        self.sink = self._p("sink", None)
+        if self.sink not in (None, "zero", "learned"):
+            raise ConfigError(f"{what}: sink='{self.sink}' (expected 'zero', 'learned' or none)")
+        self.keep_first = int(self._p("keep_first", 0) or 0)
+        if self.keep_first < 0:
+            raise ConfigError(f"{what}: keep_first={self.keep_first} must not be negative")
+        if self.keep_first and self.window is None:
+            self.keep_first = 0                              # without a window every key is read anyway
+        if self.keep_first and self.block is not None:
+            raise ConfigError(f"{what}: keep_first does not go with blocks of positions")
+
+    def _bind_sink(self, w, device):
+        if self.sink == "learned":
+            self.sink_w = w["sink"].to(torch.float32).reshape(-1).contiguous()
+        elif self.sink == "zero":
+            self.sink_w = torch.zeros(self.H, dtype=torch.float32, device=device)
+        else:
+            self.sink_w = None
+
 
     def _tile_setup(self):
         # (the split-key kernel reads keys 16 bytes at a time and shares a kv head among at most 8 query heads;
@@ -120,6 +153,7 @@ class PagedAttentionKernels:
         it); returns the heads side by side."""
         H, G, hd = self.H, self.G, self.hd
         o = torch.empty_like(q)
+        extra = dict(keep_first=self.keep_first, sink=self.sink_w)
         tiles = ctx.tables.get(self.step_tables_key)
         if self.split_ok and (tiles is None or q.dtype == torch.float32):
             # rows that each read a long cache (decode): split the keys over many CTAs.  The 32-bit path
@@ -135,13 +169,14 @@ class PagedAttentionKernels:
                 t0 = tiles.n_short_tiles
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg[t0:],
                                     tiles.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
-                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block, exact_weights=self.exact_weights)
+                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block, exact_weights=self.exact_weights,
+                                    **extra)
             else:
                 # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
                 big = (None, None) if lead else (tiles.big_tile_seg, tiles.big_tile_row0)
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
                                     tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big,
-                                    block=self.block, exact_weights=self.exact_weights)
+                                    block=self.block, exact_weights=self.exact_weights, **extra)
         else:
             lead = tiles.n_short_rows if tiles is not None else 0
             if lead and self.split_ok:
@@ -149,7 +184,7 @@ class PagedAttentionKernels:
             else:
                 lead = 0
             K.attention_rows(q[lead:], cache.tensor, view.block_table, ctx.row_seg[lead:], ctx.positions[lead:], o[lead:],
-                             self.scale, self.window, view.page_size, H, G, hd, self.block)
+                             self.scale, self.window, view.page_size, H, G, hd, self.block, **extra)
         return o
 
     def _split(self, q, o, ctx, view, cache, n_rows):
@@ -169,7 +204,7 @@ class PagedAttentionKernels:
             self.env.shared["attn_scratch"] = ws
         K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
                           o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block,
-                          self.exact_weights)
+                          self.exact_weights, keep_first=self.keep_first, sink=self.sink_w)
 
 
 class Attention(PagedAttentionKernels, Part):
@@ -222,8 +257,6 @@ class Attention(PagedAttentionKernels, Part):
         self.dim = self.hd
         self.vdim = int(self._p("value_dim", self.dim))
         if self.qk_norm == "projection" or self.vdim != self.dim:
-            if self.qk_norm_eps is not None and self.qk_norm != "projection":
-                raise ConfigError("attention: value_dim differs from head_dim, which the per-head q/k norm does not take")
             if self.values_are_keys or self.bias:
                 raise ConfigError("attention: values='keys' and biases want value_dim = head_dim and the per-head norm")
             if min(self.dim, self.vdim) < 1:
@@ -243,6 +276,19 @@ class Attention(PagedAttentionKernels, Part):
             pos = PartSpec(**pos)
         self.position = make_part("position", pos, env)
         self.graph_safe = bool(self.position.graph_safe)     # a position part that reads host values keeps it eager
+        self._read_sink("attention")
+        qt = self._p("q_temp", None)
+        self.q_temp = None
+        if qt is not None:
+            coef, every = (qt["coef"], qt["every"]) if isinstance(qt, dict) else qt
+            self.q_temp = (float(coef), float(every))
+            if not self.q_temp[1] > 0:
+                raise ConfigError(f"attention: q_temp.every={every} must be positive")
+            if not hasattr(self.position, "fused_rotary") or self.qk_norm == "projection":
+                raise ConfigError("attention: q_temp runs in the fused q/k kernel (no position part of its own, per-head norm or none)")
+        if self.vdim != self.dim and self.qk_norm != "projection" and self.qk_norm_eps is not None:
+            if not hasattr(self.position, "fused_rotary") or self.position.fused_rotary()[2]:
+                raise ConfigError("attention: a per-head q/k norm with value_dim != head_dim runs without a rotation")
         if self.values_are_keys and not hasattr(self.position, "fused_rotary"):
             raise ConfigError("attention: values='keys' needs a position encoding that runs in the fused q/k kernel")
         if self.qk_norm == "projection" and (not hasattr(self.position, "fused_rotary") or self.position.fused_rotary()[2]):
@@ -265,6 +311,8 @@ class Attention(PagedAttentionKernels, Part):
         elif self.qk_norm_eps is not None:
             s["q_norm.weight"] = WeightSpec((self.dim,), "norm")
             s["k_norm.weight"] = WeightSpec((self.dim,), "norm")
+        if self.sink == "learned":
+            s["sink"] = WeightSpec((H,), "bias")
         if self.bias:
             hd = self.hd                      # (biases go with value_dim = head_dim)
             for n, sz in (("q_proj", H * hd), ("k_proj", G * hd), ("v_proj", G * hd), ("out_proj", d)):
@@ -308,12 +356,15 @@ class Attention(PagedAttentionKernels, Part):
             if not self.borrows:
                 self.k_w = self._pad_heads(w["k_norm.weight"].float(), G, self.dim)
         elif self.qk_norm_eps is not None:
-            self.q_w = w["q_norm.weight"].float().contiguous()
-            self.k_w = w["k_norm.weight"].float().contiguous()
+            # (a head stored wider than it is: zeros behind the weight's own columns, as behind the head's)
+            self.q_w = self._pad_heads(w["q_norm.weight"].float(), 1, self.dim)
+            self.k_w = self._pad_heads(w["k_norm.weight"].float(), 1, self.dim)
+        self._bind_sink(w, self.w_qkv.device)
 
     def cache_spec(self):
         # (a borrower names what it reads, so that the engine can see that lender and borrower agree)
-        return PagedKVSpec(self.G, self.hd, self.cache_window, None if self.block is None else int(self.block))
+        return PagedKVSpec(self.G, self.hd, self.cache_window, None if self.block is None else int(self.block),
+                           self.keep_first if self.cache_window is not None else 0)
 
     def forward(self, h, residual, ctx, cache):
         """``cache``: a :class:`~kappai_b200.cache.storage.KVLayerView`."""
@@ -330,7 +381,8 @@ class Attention(PagedAttentionKernels, Part):
         elif hasattr(self.position, "fused_rotary"):
             cos, sin, rot, inter = self.position.fused_rotary()
             K.qk_norm_rope_kv(qkv, self.q_w, self.k_w, self.qk_norm_eps or 0.0, cos, sin, rot, inter,
-                              ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd, self.v_col)
+                              ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd, self.v_col,
+                              norm_dim=self.dim, q_temp=self.q_temp)
         else:
             # a position encoding of its own: norm in place, let it change q and k, then scatter
             if self.q_w is not None:
@@ -359,8 +411,11 @@ class LatentAttention(PagedAttentionKernels, Part):
     as the wider of ``head_dim`` and ``value_dim``, rounded up to a multiple of 16 (the expanding matrices, the
     gate's and the output matrix get zero rows or columns for that at load, so that nothing pads at run time).
 
+    ``gate`` = ``"head_sigmoid"``: one gate a head, ``sigmoid(h Wg^T)`` with Wg [num_heads, hidden].  ``window``,
+    ``keep_first`` and ``sink`` as in :class:`Attention` (a learned sink is the tensor ``sink`` [num_heads]).
+
     Params: hidden_size, num_heads, head_dim, value_dim, q_rank, kv_rank, scale, norm_eps, gate (None |
-    "sigmoid"), softmax_weights ("operand" | "float32"), window, block.
+    "sigmoid" | "head_sigmoid"), softmax_weights ("operand" | "float32"), window, block, keep_first, sink.
     """
 
     category = "mixer"
@@ -379,9 +434,11 @@ class LatentAttention(PagedAttentionKernels, Part):
         self.window: Optional[int] = self._p("window", None)
         self.block: Optional[int] = self._p("block", None)
         gate = self._p("gate", None)
-        if gate not in (None, "sigmoid"):
-            raise ConfigError(f"latent_attention: gate='{gate}' (expected 'sigmoid' or none)")
+        if gate not in (None, "sigmoid", "head_sigmoid"):
+            raise ConfigError(f"latent_attention: gate='{gate}' (expected 'sigmoid', 'head_sigmoid' or none)")
         self.gated = gate is not None
+        self.head_gate = gate == "head_sigmoid"
+        self._read_sink("latent_attention")
         sw = self._p("softmax_weights", "operand")
         if sw not in ("operand", "float32"):
             raise ConfigError(f"latent_attention: softmax_weights='{sw}' (expected 'operand' or 'float32')")
@@ -402,7 +459,9 @@ class LatentAttention(PagedAttentionKernels, Part):
              "k_up.weight": WeightSpec((H * self.dim, self.kv_rank)), "v_up.weight": WeightSpec((H * self.vdim, self.kv_rank)),
              "out_proj.weight": WeightSpec((d, H * self.vdim))}
         if self.gated:
-            s["gate_proj.weight"] = WeightSpec((H * self.vdim, d))
+            s["gate_proj.weight"] = WeightSpec((H if self.head_gate else H * self.vdim, d))
+        if self.sink == "learned":
+            s["sink"] = WeightSpec((H,), "bias")
         return s
 
     def _pad_rows(self, w, width):
@@ -416,7 +475,11 @@ class LatentAttention(PagedAttentionKernels, Part):
     def bind(self, w):
         rows = [w["q_down.weight"], w["kv_down.weight"]]
         if self.gated:
-            rows.append(self._pad_rows(w["gate_proj.weight"], self.vdim))
+            rows.append(w["gate_proj.weight"] if self.head_gate else self._pad_rows(w["gate_proj.weight"], self.vdim))
+        n_rows = sum(r.shape[0] for r in rows)
+        if n_rows % 8:
+            # zero rows behind the last, so that a row of the product's output starts on a 16-byte boundary
+            rows.append(torch.zeros((8 - n_rows % 8, self.d), dtype=rows[0].dtype, device=rows[0].device))
         self.w_down = torch.cat(rows, 0).contiguous()
         self.gate_col = self.q_rank + self.kv_rank
         self.q_norm_w = w["q_norm.weight"].float().contiguous()
@@ -424,9 +487,11 @@ class LatentAttention(PagedAttentionKernels, Part):
         self.w_uq = self._pad_rows(w["q_up.weight"], self.dim)
         self.w_ukv = torch.cat([self._pad_rows(w["k_up.weight"], self.dim), self._pad_rows(w["v_up.weight"], self.vdim)], 0).contiguous()
         self.w_o = self._pad_rows(w["out_proj.weight"].t().contiguous(), self.vdim).t().contiguous()
+        self._bind_sink(w, self.w_down.device)
 
     def cache_spec(self):
-        return PagedKVSpec(self.H, self.hd, self.window, None if self.block is None else int(self.block))
+        return PagedKVSpec(self.H, self.hd, self.window, None if self.block is None else int(self.block),
+                           self.keep_first if self.window is not None else 0)
 
     def forward(self, h, residual, ctx, cache):
         H, hd, n = self.H, self.hd, ctx.n_rows
@@ -442,7 +507,9 @@ class LatentAttention(PagedAttentionKernels, Part):
         K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q,
                           cache.tensor if cache.writes else None, view.page_size, H, H, hd)
         o = self._attend(q, ctx, view, cache)
-        if self.gated:
+        if self.head_gate:
+            K.head_gate(o, p[:, self.gate_col:self.gate_col + H], H, hd)
+        elif self.gated:
             K.sigmoid_gate(o, p[:, self.gate_col:self.gate_col + H * hd])
         linear(o, self.w_o, out=residual, accumulate=True)
 

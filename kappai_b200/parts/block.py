@@ -17,6 +17,14 @@ a layer costs two row-wise launches, as a pre-norm layer does.
 layer, and both sublayers read its output.  Each sublayer adds its float32
 output into the float32 residual, so the layer's sum is
 ``(x + mixer(h)) + ffn(h)``.
+
+``sandwich_residual``: ``x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x)))``:
+a norm in front of every sublayer and one behind it, before its output joins the
+residual.  The sublayer adds its float32 output into a zeroed float32 branch;
+one kernel norms the branch, adds it to the residual, clears the branch for
+its next use and, where another norm follows at once (the feed-forward's, or
+the first norm of the layer that runs next), norms the new residual for it in
+the same pass.
 """
 from __future__ import annotations
 
@@ -116,6 +124,62 @@ class ParallelResidualBlock(Part):
             self.side.forward(x, ctx)
 
 
+class SandwichResidualBlock(Part):
+    category = "block"
+    graph_safe = True
+
+    def assemble(self, mixer, ffn, mixer_norm, ffn_norm, side=None, post_norms=(None, None)):
+        p1, p2 = post_norms
+        if mixer_norm is None or p1 is None or (ffn is not None and (ffn_norm is None or p2 is None)):
+            raise ValueError("sandwich_residual: every sublayer needs a norm in front and a norm behind")
+        if any(type(n).__name__ != "RMSNorm" for n in (mixer_norm, p1, ffn_norm, p2) if n is not None):
+            raise ValueError("sandwich_residual: the norms are RMS norms")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm, self.side = mixer, ffn, mixer_norm, ffn_norm, side
+        self.mixer_post_norm, self.ffn_post_norm = p1, p2
+        return self
+
+    @staticmethod
+    def _branch(x, ctx):
+        """The float32 rows a sublayer adds its output into: one zeroed buffer a step, shared by the layers (the
+        kernel that reads a branch clears it)."""
+        y = getattr(ctx, "sandwich_branch", None)
+        if y is None or y.shape != x.shape:
+            y = torch.zeros_like(x)
+            ctx.sandwich_branch = y
+        return y
+
+    def forward(self, x, ctx, cache):
+        y = self._branch(x, ctx)
+        # the input of this layer's mixer: left by the layer before for this very residual, or made here
+        carry = getattr(ctx, "sandwich_carry", None)
+        ctx.sandwich_carry = None
+        n1 = self.mixer_norm
+        if carry is not None and carry[0] is x and carry[1] is n1:
+            h = carry[2]
+        else:
+            h = n1.forward(x)
+        self.mixer.forward(h, y, ctx, cache)
+        if self.ffn is not None:
+            n2, pn = self.ffn_norm, self.mixer_post_norm
+            h2 = torch.empty(x.shape, dtype=self.env.dtype, device=x.device)
+            K.rmsnorm_add_norm_rows(y, pn.weight, pn.eps, x, n2.weight, n2.eps, h2)
+            self.ffn.forward(h2, y, ctx)
+            last = self.ffn_post_norm
+        else:
+            last = self.mixer_post_norm
+        nxt = getattr(ctx, "next_block", None)
+        if isinstance(nxt, SandwichResidualBlock) and self.side is None:
+            nn = nxt.mixer_norm
+            h_next = torch.empty(x.shape, dtype=self.env.dtype, device=x.device)
+            K.rmsnorm_add_norm_rows(y, last.weight, last.eps, x, nn.weight, nn.eps, h_next)
+            ctx.sandwich_carry = (x, nn, h_next)
+        else:
+            K.rmsnorm_add_norm_rows(y, last.weight, last.eps, x)
+        if self.side is not None:
+            self.side.forward(x, ctx)
+
+
+register_part("block", "sandwich_residual", SandwichResidualBlock)
 register_part("block", "prenorm_residual", PreNormResidualBlock)
 register_part("block", "parallel_residual", ParallelResidualBlock)
 register_part("block", "postnorm_residual", PostNormResidualBlock)

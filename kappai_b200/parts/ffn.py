@@ -27,7 +27,11 @@ expert by its score times ``router_scale``, without renormalising;
 return their input (they have no tensors); ``shared_size``: a unit of that size
 which every row uses beside its chosen experts, its output times
 ``sigmoid(w_sg . h)``, one gate a row (``shared_gate`` = ``"sigmoid"``) or
-ungated (None).
+ungated (None).  ``routing`` = ``"sigmoid"``: the ``top`` largest logits are
+chosen and a chosen expert's weight is ``sigmoid(z)`` of its own logit times
+``router_scale``, not renormalised.  ``weight_on`` = ``"input"``: the weight
+multiplies what the expert reads, ``sum_j expert_j(w_j h)``, instead of what it
+returns (``"output"``, the default).
 """
 from __future__ import annotations
 
@@ -114,6 +118,11 @@ class MixtureOfExperts(Part):
         self.correction = bool(self._p("correction", self.routing == "softmax_all"))
         self.router_scale = float(self._p("router_scale", 1.0))
         self.n_identity = int(self._p("identity_experts", 0))
+        self.weight_on = str(self._p("weight_on", "output"))
+        if self.weight_on not in ("output", "input"):
+            raise ConfigError(f"moe: weight_on='{self.weight_on}' (expected 'output' or 'input')")
+        if self.weight_on == "input" and self.n_identity:
+            raise ConfigError("moe: weight_on='input' does not go with identity experts")
         self.E_all = self.E + self.n_identity                       # router outputs
         shared = self._p("shared_size", None)
         self.shared_ff = None if shared is None else int(shared)
@@ -125,6 +134,8 @@ class MixtureOfExperts(Part):
             raise ConfigError(f"moe: the kernels take top <= {K.MOE_MAX_TOP} and at most {K.MOE_MAX_EXPERTS} router outputs")
         if self.routing == "top_logits" and self.correction:
             raise ConfigError("moe: a correction of the choice belongs to routing='softmax_all'")
+        if self.routing == "sigmoid" and (self.router_bias or self.correction):
+            raise ConfigError("moe: routing='sigmoid' has neither a bias nor a correction")
         if self.routing == "softmax_all" and self.router_bias:
             raise ConfigError("moe: routing='softmax_all' has a correction of the choice, not a bias of the logits")
         if self.shared_gate not in (None, "sigmoid"):
@@ -181,7 +192,7 @@ class MixtureOfExperts(Part):
             logits = linear(h, self.w_router, None, out_dtype=torch.float32)
             K.moe_route(logits, self.top, idx, weights, layout, bias=self.b_router, **how)
         K.moe_experts(h, self.w_gu, self.w_down, layout, weights, self.top, residual, self.activation,
-                      n_identity=self.n_identity, idx=idx)
+                      n_identity=self.n_identity, idx=idx, weight_input=self.weight_on == "input")
         if self.ws_gu is not None:
             act = linear_swiglu(h, self.ws_gu, None, self.activation)
             if self.ws_gate is None:

@@ -6,7 +6,8 @@ bfloat16 (float32 when the whole model runs in 32-bit; the values are then the
 bfloat16 values, widened); a tensor stored in 32-bit stays so; float16 is
 widened to float32; integer tables become int32.  All problems are gathered
 into one error that lists missing tensors, unexpected tensors and wrong
-shapes (the reference aborts the load on the first of these,
+shapes; names that the model's spec lists as ignored may be there unread (the
+reference aborts the load on the first of these,
 src/model.c:124-127,152-166,3337-3341).
 """
 from __future__ import annotations
@@ -60,7 +61,8 @@ def load_weights(model, model_dir: str) -> None:
                     raise WeightError(f"tensor '{name}' appears in two files")
                 where[name] = f
         missing = sorted(n for n, ws in table.items() if n not in where and not ws.optional)
-        unexpected = sorted(n for n in where if n not in table)
+        ignored = set(getattr(model.spec, "ignored_tensors", ()))
+        unexpected = sorted(n for n in where if n not in table and n not in ignored)
         wrong = []
         for n, ws in table.items():
             if n in where:
