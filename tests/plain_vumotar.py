@@ -163,10 +163,19 @@ def route(h, router, top):
     return idx, np.take_along_axis(s, idx, axis=-1)
 
 
-def mixture(h, w, mlp):
-    """sum over the chosen experts of expert(weight * h), plus the shared unit."""
+def choice_margin(h, router, top):
+    """The gap, row by row, between the last chosen router logit and the first one left out (inf if all are chosen)."""
+    z = np.sort(h @ router.T, axis=-1)[:, ::-1]
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(len(h), np.inf)
+
+
+def mixture(h, w, mlp, margins=None):
+    """sum over the chosen experts of expert(weight * h), plus the shared unit.  ``margins`` (a list) gets the rows'
+    choice margins."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     idx, wt = route(h, w["router"], top)
+    if margins is not None:
+        margins.append(choice_margin(h, w["router"], top))
     out = np.zeros_like(h)
     for e in range(E):
         rows, col = np.nonzero(idx == e)
@@ -192,9 +201,9 @@ def layer_order(cfg):
     return list(range(a)) + list(range(a, b)) * t + list(range(b, n))
 
 
-def forward(cfg, weights, tokens, return_layers=False):
+def forward(cfg, weights, tokens, return_layers=False, margins=None):
     """Logits [n, vocab] of a whole sequence (float64); with ``return_layers`` also the residual after every
-    layer run [runs, n, width]."""
+    layer run [runs, n, width]; ``margins`` (a list) gets every mixture run's choice margins [n]."""
     eps = cfg["norm"]["eps"]
     E = weights["embed"].astype(np.float64)
     x = E[np.asarray(tokens)]
@@ -216,7 +225,7 @@ def forward(cfg, weights, tokens, return_layers=False):
         x = x + rms_norm(y, g("norm1b"), eps)
         if L.get("mlp") is not None:
             h = rms_norm(x, g("norm2"), eps)
-            x = x + rms_norm(mixture(h, sub(weights, p + "mlp."), L["mlp"]), g("norm2b"), eps)
+            x = x + rms_norm(mixture(h, sub(weights, p + "mlp."), L["mlp"], margins), g("norm2b"), eps)
         after.append(x.copy())
     logits = rms_norm(x, weights["final.norm"].astype(np.float64), eps) @ E.T
     return (logits, np.stack(after)) if return_layers else logits
@@ -226,3 +235,24 @@ def load(model_dir):
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
     return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))
+
+
+class PlainVumotar:
+    """A model folder (or a configuration and tensors) with the whole-sequence forward pass above."""
+
+    def __init__(self, model_dir=None, config=None, tensors=None):
+        if model_dir is not None:
+            self.cfg, self.w = load(model_dir)
+        else:
+            self.cfg, self.w = config, tensors
+
+    def forward(self, tokens, layers_out=None, margins=None):
+        """Logits [n, vocab]; the residual after every layer run is appended to ``layers_out`` if it is a list, every
+        mixture run's choice margins [n] to ``margins`` if it is one."""
+        logits, after = forward(self.cfg, self.w, tokens, True, margins)
+        if layers_out is not None:
+            layers_out.extend(after)
+        return logits
+
+    def logits(self, tokens):
+        return self.forward(tokens)

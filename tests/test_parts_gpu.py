@@ -54,7 +54,8 @@ class Batch:
         n_pages = sum(-(-L // page) for L in lens) + 2
         self.storage = CacheStorage(specs, [None] * len(specs), {g: n_pages for g in gks}, page, len(lens) + 1,
                                     dtype, torch.device("cuda:0"))
-        self.cache = CacheManager({g: (n_pages, page, s.window) for g, s in gks.items()}, len(lens) + 1)
+        self.cache = CacheManager({g: (n_pages, page, s.window, s.block, s.keep_first if s.window is not None else 0)
+                                   for g, s in gks.items()}, len(lens) + 1)
         self.groups = {g: page for g in gks}
         for i in range(len(lens)):
             self.cache.admit(i)
