@@ -47,6 +47,12 @@ mixer, retention, windowed attention with norms over whole projections and head 
 layer's keys and values; clamped gated units with biases; a soft cap on the logits) beside a Vekuzen model of dense
 layers of the same sizes (latent attention and lightning layers in turn), the closest design the engine has.
 
+``--design vumotar`` does the same for the Vumotar design (layers that norm every sublayer on both sides; windowed
+attention with kept first keys and one more in the softmax's denominator, causal attention with a query temperature,
+latent attention with a window, learned sinks and head gates; mixtures whose sigmoid scores weigh the experts'
+inputs, with a shared unit) beside a Tizusun model of mixture layers of the same sizes, the closest design the engine
+has (grouped-query attention with a mask, mixture feed-forwards, whole softmax weights).
+
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and
 exits with 2.
 """
@@ -459,6 +465,25 @@ def tupalorn_config(width, H, G, hd, ff):
             "layers": [{"type": t, "mixer": dict(m), "mlp": dict(mlp)} for t, m in mixers]}
 
 
+VUMOTAR_WINDOW = 1024
+VUMOTAR_KEEP = 4
+
+
+def vumotar_config(width, H, G, hd, E, top, ff_e):
+    """Three layers of the sizes of the other designs', one of each mixer: attention through a window with kept first
+    keys, causal attention with a query temperature, latent attention through a window; every feed-forward a mixture
+    with a shared unit of an expert's size."""
+    att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+           "mask": {"size": VUMOTAR_WINDOW, "keep_first": VUMOTAR_KEEP}}
+    att2 = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    latent = {"heads": H, "dim": hd, "vdim": hd, "q_rank": max(512, width // 2), "kv_rank": 512, "scale": hd ** -0.5,
+              "mask": {"size": VUMOTAR_WINDOW}}
+    moe = {"kind": "moe", "expert": {"ff": ff_e}, "router": {"experts": E, "top": top}, "shared": {"ff": ff_e}}
+    return {"architecture": "Vumotar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(moe)}
+                       for t, m in (("attention", att), ("attention_2", att2), ("latent_attention", latent))]}
+
+
 def lfm2_like_config(width, H, G, hd, ff, n_layers):
     return dict(architectures=["Lfm2ForCausalLM"], vocab_size=DESIGN_VOCAB, hidden_size=width, num_hidden_layers=n_layers,
                 num_attention_heads=H, num_key_value_heads=G, head_dim=hd, layer_types=["full_attention"] * n_layers,
@@ -504,15 +529,18 @@ def run_design(a) -> int:
 
     import kappai_b200.models.tizusun as tz
     import kappai_b200.models.vekuzen as vk
-    tz.SOFTMAX_WEIGHTS = vk.SOFTMAX_WEIGHTS = a.softmax_weights
+    import kappai_b200.models.vumotar as vm
+    tz.SOFTMAX_WEIGHTS = vk.SOFTMAX_WEIGHTS = vm.SOFTMAX_WEIGHTS = a.softmax_weights
     pk = peaks()
     T, B, ctx_len = PROMPT_LEN, a.batch, PROMPT_LEN + 256
     warmup = max(a.warmup, 3)
     steps = min(a.steps, 128)
     vekuzen = a.design == "vekuzen"
     tupalorn = a.design == "tupalorn"
+    vumotar = a.design == "vumotar"
     out = {"design": a.design.capitalize(),
-           "beside": ("dense Vekuzen layers of the same sizes" if tupalorn else "Tizusun layers of the same sizes" if vekuzen
+           "beside": ("Tizusun mixture layers of the same sizes" if vumotar else
+                      "dense Vekuzen layers of the same sizes" if tupalorn else "Tizusun layers of the same sizes" if vekuzen
                       else "LFM2 attention layers of the same sizes"), "dtype": "bf16",
            "softmax_weights": a.softmax_weights,
            "data": "synthetic: random weights, uniform random token ids", "prompt_tokens": T, "decode_batch": B,
@@ -525,7 +553,11 @@ def run_design(a) -> int:
         rec = {}
         if tupalorn:
             layers = "dddd"
-        pair = ((("tupalorn", tupalorn_config(width, H, G, hd, ff)),
+        if vumotar:
+            layers = "mmm"
+        pair = ((("vumotar", vumotar_config(width, H, G, hd, E, top, ff_e)),
+                 ("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers))) if vumotar else
+                (("tupalorn", tupalorn_config(width, H, G, hd, ff)),
                  ("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers))) if tupalorn else
                 (("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers)),
                  ("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers))) if vekuzen else
@@ -674,7 +706,7 @@ def main() -> int:
                     help="with --workload: launch every kernel on its own between CUDA events and print the device "
                          "time by kernel class (the run's throughput is then not the engine's)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
-    ap.add_argument("--design", choices=["tizusun", "vekuzen", "tupalorn"], default=None,
+    ap.add_argument("--design", choices=["tizusun", "vekuzen", "tupalorn", "vumotar"], default=None,
                     help="time another design at a few layer sizes beside the closest existing model of the same sizes "
                          "(tizusun beside LFM2 attention layers, vekuzen beside tizusun, tupalorn beside dense vekuzen layers) "
                          "(prefill, decode, device time by kernel class) instead of the default line")

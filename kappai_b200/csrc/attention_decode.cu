@@ -13,7 +13,9 @@
 //
 // Two variants, each an argument.  `keep_first` > 0: behind a window a row also reads the keys 0 .. keep_first - 1
 // of its sequence; the chunks that hold them are computed and merged in front of the window's chunks, the chunks
-// in between are skipped.  `sink` (one float32 number a query head, or null): exp(sink_h) is added to the softmax's
+// in between are skipped.  Where another kernel computes the window's chunks (the tensor-core form, which knows
+// nothing of kept keys), a second small launch of the kernel below (`front`) computes the kept keys alone, into slots
+// of their own behind the window's chunks (`slot0` on), and the merge is told where they are.  `sink` (one float32 number a query head, or null): exp(sink_h) is added to the softmax's
 // denominator, once a row, by the merge (the chunk kernels know nothing of it).
 #include "common.cuh"
 
@@ -55,7 +57,14 @@ __device__ __forceinline__ void key_range(int pos, int window, int block, int& k
 __device__ __forceinline__ int front_chunks(int first_hi, int chunk_keys, int c_lo) {
     return min(c_lo, (first_hi + chunk_keys - 1) / chunk_keys);
 }
-__device__ __forceinline__ int chunk_at(int i, int n_front, int c_lo) { return i < n_front ? i : c_lo + (i - n_front); }
+__device__ __forceinline__ int chunk_at(int i, int n_front, int c_lo, int front_slot0 = -1) {
+    return i < n_front ? (front_slot0 >= 0 ? front_slot0 + i : i) : c_lo + (i - n_front);
+}
+// (front_slot0 >= 0: the kept keys' chunks, of AD_CHUNK keys each, lie in slots of their own and hold kept keys only)
+#define AD_CHUNK_KEYS 256
+__device__ __forceinline__ int merge_front(int first_hi, int chunk_keys, int c_lo, int front_slot0) {
+    return front_slot0 >= 0 ? (first_hi + AD_CHUNK_KEYS - 1) / AD_CHUNK_KEYS : front_chunks(first_hi, chunk_keys, c_lo);
+}
 
 // HD, RR: head size and query heads per kv head fixed at compile time (loops unroll, loads overlap);
 // 0 means "taken from the arguments".
@@ -64,7 +73,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, const int* __restrict__ block_table,
                   int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
-                  int page_size, int H, int G, int hd_rt, int block, int keep_first) {
+                  int page_size, int H, int G, int hd_rt, int block, int keep_first, int slot0, int front) {
     kp_pdl_begin();
     extern __shared__ float smem[];
     const int hd = HD ? HD : hd_rt;
@@ -80,7 +89,8 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     int k_lo, k_hi;
     key_range(positions[row], window, block, k_lo, k_hi);
     const int c0 = chunk * AD_CHUNK;
-    const int first_hi = min(keep_first, k_lo);                 // keys below it are read although they lie before the window
+    int first_hi = min(keep_first, k_lo);                       // keys below it are read although they lie before the window
+    if (front) { k_hi = first_hi - 1; k_lo = 0; first_hi = 0; } // the kept keys alone (none: no chunk passes the test below)
     if (c0 > k_hi || (c0 + AD_CHUNK - 1 < k_lo && c0 >= first_hi)) return;          // the chunk holds none of this row's keys
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
     const size_t page_stride = (size_t)2 * G * page_size * hd;
@@ -222,10 +232,10 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
         const int r = e / hd, d = e % hd;
         float v = 0.f;
         for (int sl = 0; sl < n_slices; sl++) v += red[((size_t)sl * R + r) * hd + d];
-        part_acc[(((size_t)row * H + g * R + r) * n_chunks + chunk) * hd + d] = v;
+        part_acc[(((size_t)row * H + g * R + r) * n_chunks + slot0 + chunk) * hd + d] = v;
     }
     if (tid < R) {
-        float* ml = part_ml + (((size_t)row * H + g * R + tid) * n_chunks + chunk) * 2;
+        float* ml = part_ml + (((size_t)row * H + g * R + tid) * n_chunks + slot0 + chunk) * 2;
         ml[0] = stat_m[tid];
         ml[1] = stat_l[tid];
     }
@@ -243,7 +253,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                   int chunk_keys, int window, int H, int hd, int block, int keep_first,
-                                  const float* __restrict__ sink) {
+                                  const float* __restrict__ sink, int front_slot0) {
     kp_pdl_begin_early_if(gridDim.y > 1);
     extern __shared__ __align__(16) float merge_sm[];       // [MERGE_BATCH], [n_chunks] l_c, [n_chunks] exp(m_c - m), [32]
     const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
@@ -252,7 +262,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     // (a position beyond the chunks the caller gave is the caller's fault; the clamp keeps the reads inside
     // the scratch and the shared arrays all the same)
     const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi);
-    const int n_front = front_chunks(min(keep_first, k_lo), chunk_keys, c_lo), n = n_front + c_hi - c_lo + 1;
+    const int n_front = merge_front(min(keep_first, k_lo), chunk_keys, c_lo, front_slot0), n = n_front + c_hi - c_lo + 1;
     float* s_acc = merge_sm;
     float* s_l = merge_sm + MERGE_BATCH;
     float* s_w = s_l + n_chunks;
@@ -270,7 +280,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
             const int i = (k * MERGE_THREADS + tid) * 4;
             if (i < nb * hd) {
                 const int j = i / hd;                       // (hd is a multiple of 4: a float4 stays inside one chunk)
-                reg[k] = *reinterpret_cast<const float4*>(pa + (size_t)chunk_at(c0 + j, n_front, c_lo) * hd + (i - j * hd));
+                reg[k] = *reinterpret_cast<const float4*>(pa + (size_t)chunk_at(c0 + j, n_front, c_lo, front_slot0) * hd + (i - j * hd));
             }
         }
     };
@@ -278,7 +288,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
     float m = -INFINITY;
     for (int c = tid; c < n; c += nt) {
-        const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(c, n_front, c_lo));
+        const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(c, n_front, c_lo, front_slot0));
         s_w[c] = v.x;                                       // m_c for now
         s_l[c] = v.y;
         m = fmaxf(m, v.x);
@@ -321,7 +331,7 @@ template <typename T>
 __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                        int chunk_keys, int window, int H, int hd, int n_rows, int block, int keep_first,
-                                       const float* __restrict__ sink) {
+                                       const float* __restrict__ sink, int front_slot0) {
     kp_pdl_begin_early_if(n_rows > 1);
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);          // (row, head)
@@ -330,7 +340,7 @@ __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const
     int k_lo, k_hi;
     key_range(positions[row], window, block, k_lo, k_hi);
     const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi);
-    const int n_front = front_chunks(min(keep_first, k_lo), chunk_keys, c_lo), n = n_front + c_hi - c_lo + 1;
+    const int n_front = merge_front(min(keep_first, k_lo), chunk_keys, c_lo, front_slot0), n = n_front + c_hi - c_lo + 1;
     const float* pa = part_acc + ((size_t)row * H + h) * n_chunks * hd;
     const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
     // the sums of the first MERGE_WARP_BLOCK chunks are on their way while the statistics are worked out
@@ -342,13 +352,13 @@ __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int d = lane + 32 * i;
-                a[j][i] = (c0 + j < n && d < hd) ? pa[(size_t)chunk_at(c0 + j, n_front, c_lo) * hd + d] : 0.f;
+                a[j][i] = (c0 + j < n && d < hd) ? pa[(size_t)chunk_at(c0 + j, n_front, c_lo, front_slot0) * hd + d] : 0.f;
             }
     };
     fetch(0);
     float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;                       // chunks lane and lane + 32
-    if (lane < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane, n_front, c_lo)); m0 = v.x; l0 = v.y; }
-    if (lane + 32 < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane + 32, n_front, c_lo)); m1 = v.x; l1 = v.y; }
+    if (lane < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane, n_front, c_lo, front_slot0)); m0 = v.x; l0 = v.y; }
+    if (lane + 32 < n) { const float2 v = *reinterpret_cast<const float2*>(ml + 2 * chunk_at(lane + 32, n_front, c_lo, front_slot0)); m1 = v.x; l1 = v.y; }
     float m = warp_max(fmaxf(m0, m1));
     if (sink) m = fmaxf(m, sink[h]);
     const float w0 = lane < n ? expf(m0 - m) : 0.f, w1 = lane + 32 < n ? expf(m1 - m) : 0.f;
@@ -380,12 +390,13 @@ static size_t merge_smem_bytes(int n_chunks) { return sizeof(float) * ((size_t)2
 template <typename T>
 static int launch_merge(const float* part_acc, const float* part_ml, const int* positions, void* out, int ldo,
                         int n_chunks, int chunk_keys, int window, int block, int keep_first, const float* sink, int n, int H,
-                        int hd, cudaStream_t s) {
+                        int hd, cudaStream_t s, int front_slot0 = -1) {
     if (window <= 0) keep_first = 0;
+    if (keep_first == 0) front_slot0 = -1;
     if (n_chunks <= MERGE_WARP_CHUNKS && hd <= 128) {
         const int warps = 8;
         kp_launch_pdl(attn_merge_warp_kernel<T>, dim3((n * H + warps - 1) / warps), dim3(warps * 32), 0, s, part_acc, part_ml,
-                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n, block, keep_first, sink);
+                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n, block, keep_first, sink, front_slot0);
         return kp_launch_status();
     }
     const size_t smem = merge_smem_bytes(n_chunks);
@@ -396,7 +407,7 @@ static int launch_merge(const float* part_acc, const float* part_ml, const int* 
     }
     if (hd > MERGE_THREADS || (hd & 3)) return KP_ERR_UNSUPPORTED;
     kp_launch_pdl(attn_merge_kernel<T>, dim3(H, n), dim3(MERGE_THREADS), smem, s, part_acc, part_ml, positions, (T*)out, ldo,
-                  n_chunks, chunk_keys, window, H, hd, block, keep_first, sink);
+                  n_chunks, chunk_keys, window, H, hd, block, keep_first, sink, front_slot0);
     return kp_launch_status();
 }
 
@@ -432,10 +443,11 @@ int kp_attention_split_sink(const void* q, int ldq, const void* cache, const int
     float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_chunks, G, n);
+    constexpr int SLOT0 = 0, FRONT = 0;
 #define AD_LAUNCH(T, HD, RR)                                                                                      \
     kp_launch_pdl(attn_split_kernel<T, HD, RR>, dim3(grid), dim3(AD_THREADS), smem, s, (const T*)q, ldq, (const T*)cache, block_table,       \
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
-                                                                n_chunks, scale, window, page_size, H, G, hd, block, keep_first)
+                                                                n_chunks, scale, window, page_size, H, G, hd, block, keep_first, SLOT0, FRONT)
     KP_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e0;
         if (hd == 64 && R == 4) e0 = AD_LAUNCH(T, 64, 4);
@@ -466,21 +478,41 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
 
 // The merge alone, for partials of chunks of `chunk_keys` keys that another kernel wrote into `scratch` in the
 // same format.
+// The kept first keys alone, for partials whose window chunks another kernel writes: chunks of 256 keys into the slots
+// front_slot0, front_slot0 + 1, ... of a scratch of n_chunks slots a (row, head).  The merge is then given front_slot0.
+int kp_attention_front_chunks(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                              const int* row_seg, const int* positions, float* scratch, int n_chunks, int front_slot0, float scale,
+                              int window, int keep_first, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+    if (n <= 0 || keep_first <= 0 || window <= 0) return 0;
+    if (hd < 16 || hd > KP_MAX_HEAD_DIM || (hd & 15)) return KP_ERR_UNSUPPORTED;
+    if (G < 1 || H % G != 0 || H / G > AD_RMAX || page_size < 1 || n > 65535 || G > 65535) return KP_ERR_UNSUPPORTED;
+    const int n_front = (keep_first + AD_CHUNK - 1) / AD_CHUNK;
+    if (front_slot0 < 0 || front_slot0 + n_front > n_chunks) return KP_ERR_BAD_ARG;
+    const size_t smem = split_smem_bytes(H / G, hd);
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attn_split_kernel<T, 0, 0>, dim3(n_front, G, n), dim3(AD_THREADS), smem, (cudaStream_t)stream,
+                                               (const T*)q, ldq, (const T*)cache, block_table, max_blocks, row_seg, positions, part_acc,
+                                               part_ml, n_chunks, scale, window, page_size, H, G, hd, 0, keep_first, front_slot0, 1)));
+    return kp_launch_status();
+}
+
+// front_slot0: -1, or the slot from which the kept first keys' chunks lie (see kp_attention_front_chunks).
 int kp_attention_merge_sink(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
-                            int chunk_keys, int window, int block, int keep_first, const float* sink, int n, int H, int hd,
-                            int dtype, void* stream) {
+                            int chunk_keys, int window, int block, int keep_first, const float* sink, int front_slot0, int n,
+                            int H, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535 || chunk_keys < 1) return KP_ERR_UNSUPPORTED;
     const float* part_acc = scratch;
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     KP_DISPATCH_DTYPE(dtype, T, return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, chunk_keys, window,
-                                                       block, keep_first, sink, n, H, hd, (cudaStream_t)stream));
+                                                       block, keep_first, sink, n, H, hd, (cudaStream_t)stream, front_slot0));
     return kp_launch_status();
 }
 
 int kp_attention_merge_masked(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
                               int chunk_keys, int window, int block, int n, int H, int hd, int dtype, void* stream) {
-    return kp_attention_merge_sink(positions, out, ldo, scratch, n_chunks, chunk_keys, window, block, 0, nullptr, n, H, hd,
+    return kp_attention_merge_sink(positions, out, ldo, scratch, n_chunks, chunk_keys, window, block, 0, nullptr, -1, n, H, hd,
                                    dtype, stream);
 }
 

@@ -443,6 +443,59 @@ rmsnorm_add_norm_rows_kernel(float* __restrict__ y, const float* __restrict__ wb
     }
 }
 
+// The same for 16-byte aligned rows of at most 8192 floats (d % 4 == 0): a thread keeps its float4s of the row in
+// registers, so y and x are read once, and x, the cleared y and h leave in 16- and 8-byte stores.  Which form runs
+// depends on the row's length and the buffers' alignment alone, never on the rows of the step.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_norm_rows_vec_kernel(float* __restrict__ y, const float* __restrict__ wb, float eps_b, float* __restrict__ x,
+                                 const float* __restrict__ wn, float eps_n, T* __restrict__ h_out, int d) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    constexpr int PER = 8;
+    const int r = blockIdx.x, d4 = d >> 2;
+    float4* yr = reinterpret_cast<float4*>(y + (size_t)r * d);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * d);
+    float4 v[PER], xv[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < d4 ? yr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < d4) xv[j] = xr[i];
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float sb = 1.0f / sqrtf(ss / (float)d + eps_b);
+    float s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < d4) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(wb) + i);
+            float4 a;
+            a.x = xv[j].x + (v[j].x * sb) * w.x; a.y = xv[j].y + (v[j].y * sb) * w.y;
+            a.z = xv[j].z + (v[j].z * sb) * w.z; a.w = xv[j].w + (v[j].w * sb) * w.w;
+            xr[i] = a;
+            yr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            v[j] = a;
+            s2 = fmaf(a.x, a.x, s2); s2 = fmaf(a.y, a.y, s2); s2 = fmaf(a.z, a.z, s2); s2 = fmaf(a.w, a.w, s2);
+        }
+    }
+    if (h_out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float sn = 1.0f / sqrtf(s2 / (float)d + eps_n);
+    T* hr = h_out + (size_t)r * d;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < d4) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(wn) + i);
+            store4(hr + 4 * i, (v[j].x * sn) * w.x, (v[j].y * sn) * w.y, (v[j].z * sn) * w.z, (v[j].w * sn) * w.w);
+        }
+    }
+}
+
 // out[r, :] += sigmoid(h[r, :] . wg) * y[r, :]: a branch weighed by one gate a row, the gate's logit computed here
 // (float32 sum in a fixed order, h widened from its storage type).
 template <typename T>
@@ -848,6 +901,12 @@ int kp_rmsnorm_add_norm_rows(float* y, const float* wb, float eps_b, float* x, c
                              int d, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (d < 1 || ((wn == nullptr) != (h_out == nullptr))) return KP_ERR_BAD_ARG;
+    const bool vec = (d & 3) == 0 && d <= 8192 && !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)wb | (uintptr_t)wn | (uintptr_t)h_out) & 15);
+    if (vec) {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, y,
+                                                   wb, eps_b, x, wn, eps_n, (T*)h_out, d)));
+        return kp_launch_status();
+    }
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, y, wb,
                                                eps_b, x, wn, eps_n, (T*)h_out, d)));
     return kp_launch_status();

@@ -941,9 +941,11 @@ SPLIT_CHUNK_MMA = 256       # keys a chunk of its tensor-core form: 64, 128 or 2
 SPLIT_MAX_RATIO = 8        # query heads per kv head it takes
 
 
-def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
-    """Float elements of scratch that :func:`attention_split` needs."""
-    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2)
+def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int, keep_first: int = 0) -> int:
+    """Float elements of scratch that :func:`attention_split` needs (``keep_first``: with slots for the chunks of
+    that many kept first keys)."""
+    slots = n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) + -(-int(keep_first or 0) // SPLIT_CHUNK)
+    return n_rows * H * slots * (hd + 2)
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
@@ -957,28 +959,36 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     ``exact_weights``: the softmax weights enter the product with V whole (the scalar kernel always does so; the
     tensor-core form then multiplies their three bfloat16 parts one after the other) instead of rounded to bfloat16.
     ``keep_first`` / ``sink``: as in :func:`attention_rows`; the sink enters in the merge, once a row; kept first
-    keys behind a window take the scalar chunk kernel."""
+    keys behind a window are computed by a second small launch where the tensor-core form (which knows nothing of
+    them) computes the window's chunks."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
     n = q.shape[0]
     if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
         raise KernelError("attention_split: shape mismatch")
-    if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
+    keep_first = int(keep_first or 0) if window else 0
+    if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks, keep_first):
         raise KernelError("attention_split: scratch too small")
     _check_sink(sink, H, keep_first, window, block, "attention_split")
-    keep_first = int(keep_first or 0) if window else 0
     lib = load_library("attention_decode")
-    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0 and not keep_first:
-        # tensor-core chunk pass over smaller chunks, then the same merge
-        parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
+    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
+        # tensor-core chunk pass over smaller chunks, then the same merge; kept first keys get slots behind the window's
+        # chunks (for the chunk pass they are chunks beyond every position: it leaves them alone)
+        front0 = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
+        parts = front0 + -(-keep_first // SPLIT_CHUNK)
+        if keep_first:
+            _run("attention_front_chunks", lib.kp_attention_front_chunks, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
+                 block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(scratch), parts, front0, ctypes.c_float(scale),
+                 int(window), keep_first, page_size, n, H, G, hd, dtype_code(q.dtype), STREAM)
         _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma_masked,
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), int(block or 0),
             int(bool(exact_weights)), page_size, n, H, G, hd, STREAM)
         _run("attention_merge", lib.kp_attention_merge_sink, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
-             parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), 0, _ptr(sink), n, H, hd, dtype_code(q.dtype), STREAM)
+             parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), keep_first, _ptr(sink), front0 if keep_first else -1, n, H, hd,
+             dtype_code(q.dtype), STREAM)
         return out
     _run("attention_split", lib.kp_attention_split_sink, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
          block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),

@@ -191,7 +191,7 @@ class PagedAttentionKernels:
         """Split-key attention for the first ``n_rows`` rows of the step."""
         H, G, hd = self.H, self.G, self.hd
         n_chunks = -(-ctx.max_context // K.SPLIT_CHUNK)
-        need = K.attention_split_scratch(n_rows, H, hd, n_chunks)
+        need = K.attention_split_scratch(n_rows, H, hd, n_chunks, self.keep_first)
         ws = self.env.shared.get("attn_scratch")
         if ws is None or ws.numel() < need:
             # A captured decode step keeps the address of the scratch it was captured with, so a buffer that

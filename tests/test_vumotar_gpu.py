@@ -92,7 +92,7 @@ def test_decoded_rows_with_kept_first_keys_and_sinks(dtype, H, G, hd, page, wind
     close(host(gen).reshape(want.shape), want, dtype)
     if H // G <= Kn.SPLIT_MAX_RATIO and hd % 16 == 0:
         for n_chunks in (-(-max(seq_lens) // Kn.SPLIT_CHUNK), 7):
-            ws = torch.full((Kn.attention_split_scratch(len(pos), H, hd, n_chunks),), float("nan"), device=DEV)
+            ws = torch.full((Kn.attention_split_scratch(len(pos), H, hd, n_chunks, keep),), float("nan"), device=DEV)
             out = torch.empty_like(gen)
             Kn.attention_split(*args, out, ws, n_chunks, scale, window, page, H, G, hd, exact_weights=True, keep_first=keep, sink=sink_t)
             close(host(out).reshape(want.shape), want, dtype)
@@ -164,7 +164,7 @@ def test_one_score_stands_out(which, dtype):
     gen = torch.empty((1, H * hd), dtype=dtype, device=DEV)
     Kn.attention_rows(qr[-1:], dev(cache, dtype), i32(bt), i32([0]), i32([L - 1]), gen, 1.0, window, page, H, G, hd, keep_first=keep, sink=dev(sk))
     close(host(gen).reshape(H, hd), want, dtype)
-    ws = torch.zeros(Kn.attention_split_scratch(1, H, hd, 3), device=DEV)
+    ws = torch.zeros(Kn.attention_split_scratch(1, H, hd, 3, keep), device=DEV)
     out = torch.empty_like(gen)
     Kn.attention_split(qr[-1:], dev(cache, dtype), i32(bt), i32([0]), i32([L - 1]), out, ws, 3, 1.0, window, page, H, G, hd,
                        exact_weights=True, keep_first=keep, sink=dev(sk))
