@@ -22,7 +22,8 @@ This file is the only place that knows the design's ``config.json`` keys and ten
 layers, each with its ``type`` (the mixer), the mixer's sizes (``mixer``) and its feed-forward (``mlp``, or null
 for none); layer i's tensors start with ``l<i>.``.  Every size and constant is read from there; what the design
 fixes (the activation, the kinds of sink and gate, the place of the norms, the tied head) is written below.
-``loop``, ``mask.keep_first`` and an ``mlp``'s ``shared`` may be left out.
+``loop``, ``mask.keep_first`` and an ``mlp``'s ``shared`` may be left out; a mixer without ``mask`` reads every
+earlier key, one without ``q_temp`` has no temperature.
 """
 from __future__ import annotations
 
@@ -92,19 +93,18 @@ class VumotarConfig(TypedConfig):
             H = _int(m, "heads", mw)
             _int(m, "dim", mw), _int(m, "vdim", mw)
             _get(m, "scale", mw)
+            if m.get("mask") is not None:
+                _int(m["mask"], "size", mw + ".mask")
+                if m["mask"].get("keep_first") is not None:
+                    _int(m["mask"], "keep_first", mw + ".mask", 0)
             if kind == "latent_attention":
                 _int(m, "q_rank", mw), _int(m, "kv_rank", mw)
-                _int(m.get("mask"), "size", mw + ".mask")
             else:
                 G = _int(m, "kv_heads", mw)
                 if H % G:
                     raise ConfigError(f"{mw}: heads={H} must be a multiple of kv_heads={G}")
-            if kind == "attention":
-                _int(m.get("mask"), "size", mw + ".mask")
-                if m["mask"].get("keep_first") is not None:
-                    _int(m["mask"], "keep_first", mw + ".mask", 0)
-            if kind == "attention_2":
-                qt, qw = m.get("q_temp"), mw + ".q_temp"
+            if m.get("q_temp") is not None:
+                qt, qw = m["q_temp"], mw + ".q_temp"
                 _get(qt, "coef", qw)
                 if not float(_get(qt, "every", qw)) > 0:
                     raise ConfigError(f"{qw}.every must be positive")
@@ -122,15 +122,22 @@ class VumotarConfig(TypedConfig):
                     _int(mlp["shared"], "ff", where + ".mlp.shared")
 
 
+def _mask(m: Dict[str, Any]):
+    """(window, kept first keys) of a mixer; (None, 0) where it has no mask: every earlier key is read."""
+    mask = m.get("mask")
+    return (None, 0) if mask is None else (int(mask["size"]), int(mask.get("keep_first") or 0))
+
+
 def _mixer_spec(c: VumotarConfig, layer: Dict[str, Any], prefix: str) -> PartSpec:
     m, kind = layer["mixer"], layer["type"]
+    window, keep = _mask(m)
     common = {"hidden_size": c.width, "num_heads": int(m["heads"]), "head_dim": int(m["dim"]), "value_dim": int(m["vdim"]),
               "scale": float(m["scale"]), "softmax_weights": SOFTMAX_WEIGHTS}
     if kind == "latent_attention":
         return PartSpec(
             "latent_attention",
             dict(common, q_rank=int(m["q_rank"]), kv_rank=int(m["kv_rank"]), norm_eps=c.eps, gate="head_sigmoid",
-                 window=int(m["mask"]["size"]), sink="learned"),
+                 window=window, keep_first=keep, sink="learned"),
             prefix,
             rename={"q_down.weight": "dq", "q_norm.weight": "dq.norm", "q_up.weight": "uq", "kv_down.weight": "dkv",
                     "kv_norm.weight": "dkv.norm", "k_up.weight": "uk", "v_up.weight": "uv", "gate_proj.weight": "g",
@@ -141,12 +148,11 @@ def _mixer_spec(c: VumotarConfig, layer: Dict[str, Any], prefix: str) -> PartSpe
         rename.update({"q_norm.weight": "q.norm", "k_norm.weight": "k.norm"})
         return PartSpec(
             "attention",
-            dict(common, qk_norm="per_head", qk_norm_eps=c.eps, window=int(m["mask"]["size"]),
-                 keep_first=int(m["mask"].get("keep_first") or 0), sink="zero"),
+            dict(common, qk_norm="per_head", qk_norm_eps=c.eps, window=window, keep_first=keep, sink="zero"),
             prefix, rename=rename)
-    qt = m["q_temp"]
-    return PartSpec("attention", dict(common, qk_norm_eps=None, window=None,
-                                      q_temp={"coef": float(qt["coef"]), "every": float(qt["every"])}),
+    qt = m.get("q_temp")
+    return PartSpec("attention", dict(common, qk_norm_eps=None, window=window, keep_first=keep,
+                                      q_temp=None if qt is None else {"coef": float(qt["coef"]), "every": float(qt["every"])}),
                     prefix, rename=rename)
 
 

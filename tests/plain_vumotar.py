@@ -113,6 +113,12 @@ def grouped_attention(q, k, v, scale, mask, sink=None):
     return out.reshape(n, -1)
 
 
+def mixer_mask(n, m):
+    """The keys a mixer's rows see: its ``mask`` (a window, with kept first keys), or every earlier key."""
+    mask = m.get("mask")
+    return visible(n) if not mask else visible(n, mask["size"], mask.get("keep_first") or 0)
+
+
 def windowed_sink_attention(h, w, m, eps):
     """The mixer 'attention': per-head q/k norm, window with kept first positions, one more in the denominator."""
     n = h.shape[0]
@@ -120,8 +126,7 @@ def windowed_sink_attention(h, w, m, eps):
     q = rms_norm((h @ w["q"].T).reshape(n, H, dim), w["q.norm"], eps)
     k = rms_norm((h @ w["k"].T).reshape(n, G, dim), w["k.norm"], eps)
     v = (h @ w["v"].T).reshape(n, G, vdim)
-    mask = visible(n, m["mask"]["size"], m["mask"].get("keep_first", 0))
-    o = grouped_attention(q, k, v, m["scale"], mask, sink=np.zeros(H))
+    o = grouped_attention(q, k, v, m["scale"], mixer_mask(n, m), sink=np.zeros(H))
     return o @ w["o"].T
 
 
@@ -129,10 +134,12 @@ def tempered_attention(h, w, m):
     """The mixer 'attention_2': causal, plain softmax, queries scaled by position."""
     n = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).reshape(n, H, dim) * query_temperature(n, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    q = (h @ w["q"].T).reshape(n, H, dim)
+    if m.get("q_temp"):
+        q = q * query_temperature(n, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
     k = (h @ w["k"].T).reshape(n, G, dim)
     v = (h @ w["v"].T).reshape(n, G, vdim)
-    o = grouped_attention(q, k, v, m["scale"], visible(n))
+    o = grouped_attention(q, k, v, m["scale"], mixer_mask(n, m))
     return o @ w["o"].T
 
 
@@ -145,7 +152,7 @@ def latent_attention(h, w, m, eps):
     c = rms_norm(h @ w["dkv"].T, w["dkv.norm"], eps)
     k = (c @ w["uk"].T).reshape(n, H, dim)
     v = (c @ w["uv"].T).reshape(n, H, vdim)
-    o = grouped_attention(q, k, v, m["scale"], visible(n, m["mask"]["size"], 0), sink=w["sink"])
+    o = grouped_attention(q, k, v, m["scale"], mixer_mask(n, m), sink=w["sink"])
     gate = sigmoid(h @ w["g"].T)                                   # [n, H]
     o = (o.reshape(n, H, vdim) * gate[:, :, None]).reshape(n, -1)
     return o @ w["o"].T

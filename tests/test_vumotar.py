@@ -45,13 +45,11 @@ def test_order_of_layer_runs_and_what_every_run_keeps(name):
     assert not any(e.enter or e.cache_of is not None for e in m.schedule)     # every pass with caches of its own
     for i, s in zip(order, m.cache_specs()):
         layer, mix = cfg["layers"][i], cfg["layers"][i]["mixer"]
-        assert isinstance(s, PagedKVSpec) and s.head_dim >= max(mix["dim"], mix["vdim"]) and s.head_dim % 16 == 0
-        if layer["type"] == "attention":
-            assert (s.num_kv_heads, s.window, s.keep_first) == (mix["kv_heads"], mix["mask"]["size"], mix["mask"].get("keep_first", 0))
-        elif layer["type"] == "attention_2":
-            assert (s.num_kv_heads, s.window, s.keep_first) == (mix["kv_heads"], None, 0)
-        else:
-            assert (s.num_kv_heads, s.window, s.keep_first) == (mix["heads"], mix["mask"]["size"], 0)
+        assert isinstance(s, PagedKVSpec) and s.head_dim >= max(mix["dim"], mix["vdim"])
+        assert s.head_dim % 16 == 0 or s.head_dim == mix["dim"] == mix["vdim"]     # a head is widened only where its two sizes differ
+        mask = mix.get("mask") or {}
+        assert s.num_kv_heads == (mix["heads"] if layer["type"] == "latent_attention" else mix["kv_heads"])
+        assert (s.window, s.keep_first) == (mask.get("size"), mask.get("keep_first", 0) if mask else 0)
 
 
 def test_parts_and_their_constants_come_from_the_configuration():
@@ -75,11 +73,10 @@ def test_parts_and_their_constants_come_from_the_configuration():
     (lambda c: c.pop("vocab"), "vocab"),
     (lambda c: c["norm"].pop("eps"), "norm.eps"),
     (lambda c: c["layers"][0].update(type="conv"), "type"),
-    (lambda c: c["layers"][0]["mixer"].pop("q_temp"), "q_temp"),
     (lambda c: c["layers"][0]["mixer"]["q_temp"].update(every=0), "every"),
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "kv_heads"),
     (lambda c: c["layers"][1]["mixer"].pop("scale"), "scale"),
-    (lambda c: c["layers"][1]["mixer"].pop("mask"), "mask"),
+    (lambda c: c["layers"][0]["mixer"]["q_temp"].pop("coef"), "coef"),
     (lambda c: c["layers"][1]["mixer"]["mask"].update(keep_first=-1), "keep_first"),
     (lambda c: c["layers"][2]["mixer"].pop("kv_rank"), "kv_rank"),
     (lambda c: c["layers"][2]["mixer"]["mask"].update(size=0), "size"),
@@ -96,6 +93,17 @@ def test_configuration_errors_name_the_key(change, word):
     with pytest.raises(ConfigError) as e:
         _spec(cfg)
     assert word in str(e.value)
+
+
+def test_a_mixer_without_a_mask_reads_every_key_and_one_without_a_temperature_has_none():
+    cfg = copy.deepcopy(CONFIGS["A"][0])
+    cfg["layers"][0]["mixer"].pop("q_temp")
+    cfg["layers"][1]["mixer"].pop("mask")
+    cfg["layers"][2]["mixer"].pop("mask")
+    m = _model(cfg)
+    assert m.blocks[0].mixer.q_temp is None
+    assert m.blocks[1].mixer.window is None and m.blocks[1].mixer.keep_first == 0 and m.blocks[1].mixer.sink == "zero"
+    assert m.blocks[2].mixer.window is None and m.cache_specs()[2].window is None
 
 
 def test_parts_refuse_what_they_cannot_do():

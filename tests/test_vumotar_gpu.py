@@ -520,15 +520,15 @@ def _expect(plain, name, toks):
 
 # lengths above the longest window of every model (A: 25, B: 33, C: 2, D: 128, E: 50) plus the decoded tail, a request of
 # two or three tokens, and lengths that end on and one behind a page's last token
-LENGTHS = {"A": [150, 3, 64, 49], "B": [130, 41, 2, 97], "C": [77, 20, 101], "D": [330, 65, 201], "E": [200, 64, 140]}
-PROMPTS = {"A": [30, 1, 60, 48], "B": [50, 40, 1, 80], "C": [40, 19, 60], "D": [150, 3, 128], "E": [150, 63, 30]}
-N_LAST = {"A": 110, "B": 60, "C": 40, "D": 170, "E": 70}       # the windows pass over decoded tokens only (D: 128 + 40)
+LENGTHS = {"A": [150, 3, 64, 49], "B": [130, 41, 2, 97], "C": [77, 20, 101], "D": [330, 65, 201], "E": [200, 64, 140], "F": [90, 33, 2]}
+PROMPTS = {"A": [30, 1, 60, 48], "B": [50, 40, 1, 80], "C": [40, 19, 60], "D": [150, 3, 128], "E": [150, 63, 30], "F": [40, 32, 1]}
+N_LAST = {"A": 110, "B": 60, "C": 40, "D": 170, "E": 70, "F": 30}       # the windows pass over decoded tokens only (D: 128 + 40)
 BF16_REL_RMS = 0.04    # a row's 16-bit error (rms over the vocabulary / the row's spread): 95 % of the rows; 99 % twice that
 BF16_BETWEEN_CUTS = 0.06
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("A", 16), ("B", None), ("C", 32), ("D", None), ("E", 8)])
+@pytest.mark.parametrize("name,page_size", [("A", 16), ("B", None), ("C", 32), ("D", None), ("E", 8), ("F", 16)])
 def test_every_cut_agrees_with_plain(name, page_size, dtype, vum_dirs, vum_plain, tmp_path):
     """Whole prompts, the last tokens decoded one by one (more of them than the longest window), portions down to two
     tokens, and up to four requests mixed in a pool so small that pages and slots go round."""
@@ -574,7 +574,7 @@ def test_every_cut_agrees_with_plain(name, page_size, dtype, vum_dirs, vum_plain
                 assert np.array_equal(rows[0], x), f"{name}: float32 logits of {place} differ between cuts"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_residual_after_every_layer_run(name, vum_dirs, vum_plain):
     from kappai_b200 import ModelRunner, StepEntry
     plain = vum_plain[name]

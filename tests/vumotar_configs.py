@@ -10,23 +10,27 @@ import numpy as np
 
 
 def _attention(heads, kv_heads, dim, vdim, window, keep_first=None, scale=None):
-    mask = {"size": window}
-    if keep_first is not None:
-        mask["keep_first"] = keep_first
-    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": mask,
-                                           "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    if window is not None:
+        m["mask"] = {"size": window}
+        if keep_first is not None:
+            m["mask"]["keep_first"] = keep_first
+    return {"type": "attention", "mixer": m}
 
 
 def _attention_2(heads, kv_heads, dim, vdim, coef, every, scale=None):
-    return {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
-                                             "q_temp": {"coef": coef, "every": every},
-                                             "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    if coef is not None:
+        m["q_temp"] = {"coef": coef, "every": every}
+    return {"type": "attention_2", "mixer": m}
 
 
 def _latent(heads, dim, vdim, q_rank, kv_rank, window, scale=None):
-    return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
-                                                  "mask": {"size": window},
-                                                  "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}}
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+         "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    if window is not None:
+        m["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": m}
 
 
 def _layer(mixer, experts=None, top=None, ff=None, shared=None):
@@ -64,12 +68,12 @@ VUM_B = _model(97, 48, [
     _layer(_latent(3, 8, 24, 16, 12, 7), 3, 1, 40, 16),
     _layer(_attention_2(3, 3, 24, 8, 1.5, 6.5, 0.15), 5, 2, 24),
 ], eps=1e-6, loop=(0, 2, 3), max_positions=400)
-# C: sizes the fast kernels refuse (width 36, a vocabulary smaller than a warp, five query heads on one key head, odd
+# C: sizes the fast kernels refuse (width 38, a vocabulary smaller than a warp, five query heads on one key head, odd
 # ranks); a window of two with five kept keys (more than the window); a latent window of one; every expert chosen; a
 # temperature that changes at every position
-VUM_C = _model(19, 36, [
+VUM_C = _model(19, 38, [
     _layer(_attention(5, 1, 8, 12, 2, 5, 0.5), 3, 3, 20, 12),
-    _layer(_latent(1, 36, 12, 9, 7, 1), 2, 1, 28),
+    _layer(_latent(1, 38, 12, 9, 7, 1), 2, 1, 28),
     _layer(_attention_2(5, 1, 8, 12, 0.25, 1), 4, 2, 44, 20),
 ], eps=1e-3)
 # D: widths at which the decode products stream their weights and the prompt products run on tcgen05; head sizes 64 and
@@ -89,7 +93,15 @@ VUM_E = _model(300, 256, [
     _layer(_attention_2(16, 1, 32, 48, 0.3, 32), 2, 2, 96, 32),
 ], loop=(1, 3, 1), max_positions=640)
 
-CONFIGS = {"A": (VUM_A, 3), "B": (VUM_B, 4), "C": (VUM_C, 5), "D": (VUM_D, 6), "E": (VUM_E, 7)}
+# F: what may be left out is left out: mixers without masks (every earlier key is read, the sinks stay), no temperature,
+# no loop, no shared unit; one layer, run twice by a loop over itself, in the middle
+VUM_F = _model(64, 32, [
+    _layer(_attention(2, 1, 16, 16, None), 4, 2, 16),
+    _layer(_latent(2, 16, 8, 12, 20, None), 3, 1, 24),
+    _layer(_attention_2(4, 4, 8, 8, None, None), None),
+], loop=(1, 2, 2))
+
+CONFIGS = {"A": (VUM_A, 3), "B": (VUM_B, 4), "C": (VUM_C, 5), "D": (VUM_D, 6), "E": (VUM_E, 7), "F": (VUM_F, 8)}
 
 
 def tensor_shapes(cfg):
