@@ -445,14 +445,14 @@ rmsnorm_add_norm_rows_kernel(float* __restrict__ y, const float* __restrict__ wb
 
 // The same for 16-byte aligned rows of at most 8192 floats (d % 4 == 0): a thread keeps its float4s of the row in
 // registers, so y and x are read once, and x, the cleared y and h leave in 16- and 8-byte stores.  Which form runs
-// depends on the row's length and the buffers' alignment alone, never on the rows of the step.
-template <typename T>
+// depends on the row's length and the buffers' alignment alone, never on the rows of the step.  PER: float4s a thread
+// (2, 4 or 8 by the row's length: the fewer registers hold the row, the more rows an SM has in flight).
+template <typename T, int PER>
 __global__ void __launch_bounds__(256)
 rmsnorm_add_norm_rows_vec_kernel(float* __restrict__ y, const float* __restrict__ wb, float eps_b, float* __restrict__ x,
                                  const float* __restrict__ wn, float eps_n, T* __restrict__ h_out, int d) {
     kp_pdl_begin();
     __shared__ float red[32];
-    constexpr int PER = 8;
     const int r = blockIdx.x, d4 = d >> 2;
     float4* yr = reinterpret_cast<float4*>(y + (size_t)r * d);
     float4* xr = reinterpret_cast<float4*>(x + (size_t)r * d);
@@ -903,8 +903,13 @@ int kp_rmsnorm_add_norm_rows(float* y, const float* wb, float eps_b, float* x, c
     if (d < 1 || ((wn == nullptr) != (h_out == nullptr))) return KP_ERR_BAD_ARG;
     const bool vec = (d & 3) == 0 && d <= 8192 && !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)wb | (uintptr_t)wn | (uintptr_t)h_out) & 15);
     if (vec) {
-        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, y,
-                                                   wb, eps_b, x, wn, eps_n, (T*)h_out, d)));
+#define RMS_ADD_VEC(PER)                                                                                                   \
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_vec_kernel<T, PER>, dim3(n), dim3(256), 0, (cudaStream_t)stream, \
+                                                   y, wb, eps_b, x, wn, eps_n, (T*)h_out, d)))
+        if (d <= 2048) RMS_ADD_VEC(2);
+        else if (d <= 4096) RMS_ADD_VEC(4);
+        else RMS_ADD_VEC(8);
+#undef RMS_ADD_VEC
         return kp_launch_status();
     }
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_add_norm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, y, wb,
