@@ -40,7 +40,8 @@ sequence stay visible to every later row, at their true places, and their pages 
 ``"learned"`` adds ``exp(sink_h)`` of a tensor ``sink`` [num_heads] (not scaled, counted once a row);
 ``q_temp`` = {coef, every}: the query of position p is multiplied by
 ``1 + coef ln(floor((p + 1) / every) + 1)`` (float32, in the fused q/k kernel).  The per-head q/k norm goes with a
-``value_dim`` of its own: the norm's mean is then taken over ``head_dim`` columns of the wider cache head.
+``value_dim`` of its own: the norm's mean is then taken over ``head_dim`` columns of the wider cache head.  An odd
+``head_dim`` without a position encoding is stored wider in the same way.
 
 Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
 value_dim, scale, qk_norm_eps (None: no q/k norm), qk_norm ("per_head" |
@@ -256,7 +257,9 @@ class Attention(PagedAttentionKernels, Part):
         # dim, vdim: the heads as the model has them; hd: as the cache and the kernels see them
         self.dim = self.hd
         self.vdim = int(self._p("value_dim", self.dim))
-        if self.qk_norm == "projection" or self.vdim != self.dim:
+        pos_given = self._p("position", None) is not None
+        if self.qk_norm == "projection" or self.vdim != self.dim or (self.dim % 2 and not pos_given):
+            # (an odd head size without a rotation is stored wider too: the kernels take even sizes)
             if self.values_are_keys or self.bias:
                 raise ConfigError("attention: values='keys' and biases want value_dim = head_dim and the per-head norm")
             if min(self.dim, self.vdim) < 1:

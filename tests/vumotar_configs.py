@@ -68,13 +68,13 @@ VUM_B = _model(97, 48, [
     _layer(_latent(3, 8, 24, 16, 12, 7), 3, 1, 40, 16),
     _layer(_attention_2(3, 3, 24, 8, 1.5, 6.5, 0.15), 5, 2, 24),
 ], eps=1e-6, loop=(0, 2, 3), max_positions=400)
-# C: sizes the fast kernels refuse (width 38, a vocabulary smaller than a warp, five query heads on one key head, odd
+# C: sizes the fast kernels refuse (an odd width, odd head sizes, a vocabulary smaller than a warp, five query heads on one key head, odd
 # ranks); a window of two with five kept keys (more than the window); a latent window of one; every expert chosen; a
 # temperature that changes at every position
-VUM_C = _model(19, 38, [
+VUM_C = _model(19, 37, [
     _layer(_attention(5, 1, 8, 12, 2, 5, 0.5), 3, 3, 20, 12),
-    _layer(_latent(1, 38, 12, 9, 7, 1), 2, 1, 28),
-    _layer(_attention_2(5, 1, 8, 12, 0.25, 1), 4, 2, 44, 20),
+    _layer(_latent(1, 37, 12, 9, 7, 1), 2, 1, 28),
+    _layer(_attention_2(5, 1, 7, 7, 0.25, 1), 4, 2, 44, 20),
 ], eps=1e-3)
 # D: widths at which the decode products stream their weights and the prompt products run on tcgen05; head sizes 64 and
 # 128 (tensor-core attention kernels) with 70 kept keys (more than a key tile) behind a window of two pages; prompts
